@@ -1,0 +1,221 @@
+/*
+ * void_b200 — C ABI of the B200 (sm_100a) quantized block-sparse SpMM path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, returns 0
+ * (VOID_OK) or a negative status, never throws, never synchronises the stream and never
+ * allocates device memory: workspaces are passed in by the caller.  The functions are what
+ * a foreign-function binding of the reference's Python operators would bind; each comment
+ * names the reference code (path inside the Khushiyant/void project) that the entry point
+ * replaces.
+ *
+ * Vocabulary: a *tile* is one stored 32x32 block of A; a *tile row* is one row of the
+ * block grid (32 matrix rows); a *panel* is a 32(k) x 128(n) slab of B; the *packed* form
+ * of A is its tiles in tile-row-major order, 1024 bytes each, in the core-matrix order the
+ * tensor cores read from shared memory.
+ */
+#ifndef VOID_B200_H_
+#define VOID_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VOID_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define VOID_API __attribute__((visibility("default")))
+#else
+#define VOID_API
+#endif
+
+/* status codes */
+enum {
+  VOID_OK = 0,
+  VOID_ERR_BAD_ARG = -1,        /* null pointer, negative size, unknown enum value      */
+  VOID_ERR_ALIGN = -2,          /* pointer or leading dimension breaks an alignment rule */
+  VOID_ERR_SHAPE = -3,          /* sizes that the kernels do not support                 */
+  VOID_ERR_ARCH = -4,           /* current device is not sm_100                          */
+  VOID_ERR_CUDA = -5,           /* a CUDA runtime / driver call failed                   */
+  VOID_ERR_WORKSPACE = -6,      /* caller workspace too small                            */
+  VOID_ERR_DEVICE_TIMEOUT = -7, /* a bounded device-side wait gave up (see status word)  */
+  VOID_ERR_TOO_LARGE = -8       /* size beyond a documented maximum                      */
+};
+
+/* element kinds of the 8-bit operands */
+enum { VOID_KIND_I8 = 0, VOID_KIND_F8E4M3 = 1 };
+/* output element types */
+enum { VOID_OUT_F32 = 0, VOID_OUT_F16 = 1, VOID_OUT_BF16 = 2 };
+/* epilogue activation codes; same numbering as get_activation_code, void/fusion.py:77-91 */
+enum { VOID_ACT_NONE = 0, VOID_ACT_RELU = 1, VOID_ACT_GELU = 2, VOID_ACT_SILU = 3 };
+/* how tile scales enter the result */
+enum {
+  VOID_SCALE_ROW_MEAN = 0, /* whole tile row in one accumulator, times the MEAN of the row's
+                              tile scales: void/int_quant.py:479-481, :516-526            */
+  VOID_SCALE_PER_TILE = 1  /* every tile's product is scaled by its own scale before it is
+                              added: void/fp8.py:638-646, :657-659                        */
+};
+
+typedef void* void_stream_t; /* a cudaStream_t */
+
+VOID_API const char* void_strerror(int status);
+VOID_API int void_b200_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Tile index.  Replaces VOIDTensor.get_row_block_info, void/format.py:201-237 (same code in
+ * void/int_quant.py:158-175 and void/fp8.py:712-720): row_ptr[nbr+1] = exclusive prefix sum
+ * of tiles per tile row, block_indices[nnz] = argsort of (block_row * nbc + block_col).
+ * Keys are unique, so the result is bit-exact with the reference's torch.argsort.
+ * ws: caller workspace of void_tile_index_ws_bytes(nbr, nbc) bytes (a bitmap of the block
+ * grid plus per-row counters).
+ * ------------------------------------------------------------------------------------- */
+VOID_API size_t void_tile_index_ws_bytes(int32_t nbr, int32_t nbc);
+VOID_API int void_build_tile_index(const int32_t* block_rows, const int32_t* block_cols, int64_t nnz,
+                          int32_t nbr, int32_t nbc, int32_t* row_ptr, int32_t* block_indices,
+                          void* ws, size_t ws_bytes, void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Pack.  Gathers the Morton-ordered 8-bit tiles (Int8VOIDTensor.values,
+ * void/int_quant.py:116, or FP8VOIDTensor.values_fp8, void/fp8.py:445) into tile-row-major
+ * order through block_indices and rewrites each 32x32 tile into 8x16-byte core matrices.
+ * Also gathers tile_cols = block_cols[block_indices], tile_scales = scales[block_indices]
+ * and row_scale[r] = (sum of the row's tile scales, added in row order) / count — the
+ * reference's avg_scale for b_scale = 1, void/int_quant.py:516-526.  scales may hold one
+ * value for all tiles (n_scales == 1, per-tensor mode).
+ * packed must be 1024-byte aligned and hold nnz*1024 bytes.
+ * ------------------------------------------------------------------------------------- */
+VOID_API int void_pack_tiles(const void* values, const float* scales, int64_t n_scales,
+                    const int32_t* block_cols, const int32_t* block_indices,
+                    const int32_t* row_ptr, int64_t nnz, int32_t nbr, void* packed,
+                    int32_t* tile_cols, float* tile_scales, float* row_scale,
+                    void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Quantisers.
+ * void_quant_i8_tiles: per-tile symmetric INT8, scale = max(absmax/128, 1e-8),
+ *   q = clamp(rint(x / scale), -128, 127): quantize_void_tensor / quantize_tensor /
+ *   compute_scale_minmax, void/int_quant.py:328-388, :254-305, :178-214.
+ * void_quant_fp8_tiles: per-tile E4M3, scale = max(amax/448, 1e-12), scale_inv = 1/scale,
+ *   q = e4m3_rn(clamp(x * scale_inv, -448, 448)): quantize_to_fp8 with a fresh amax
+ *   history, void/fp8.py:185-229, :91-105.
+ * void_quant_cols: the same two formulas along the columns of a row-major [K,N] fp32
+ *   matrix (per-column scales of B); the reference reaches this through
+ *   quantize_tensor(B.T, PER_CHANNEL), void/int_quant.py:273-274, and
+ *   quantize_to_fp8(B.T, per_row), void/fp8.py:177-180.  q is [K, ldq] bytes.
+ * ------------------------------------------------------------------------------------- */
+VOID_API int void_quant_i8_tiles(const float* values, int64_t nnz, int8_t* q, float* scales,
+                        void_stream_t stream);
+VOID_API int void_quant_fp8_tiles(const float* values, int64_t nnz, uint8_t* q, float* scale,
+                         float* scale_inv, float* amax, void_stream_t stream);
+VOID_API int void_quant_cols(const float* b, int64_t ldb, int32_t K, int32_t N, int32_t kind, void* q,
+                    int64_t ldq, float* col_scale, float* col_scale_inv,
+                    void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Work plan.  A *segment* is a run of consecutive tiles of one tile row that one CTA
+ * accumulates in tensor memory; a row cut into several segments is finished by the CTA
+ * that arrives last (integer partial sums, so the result does not depend on arrival order).
+ *
+ * void_streamk_table reproduces compute_stream_k_workload, void/stream_k.py:36-110, on the
+ * device: rows in order, each non-empty row cut into chunks of
+ * target = min(ceil(nnz / n_workers), max_work) tiles; needs_atomic = chunk is not the
+ * whole row.  n_workers_req <= 0 selects the reference default min(nnz, 1024).  The four
+ * output arrays need capacity void_streamk_table_capacity(nnz, nbr) entries; the realised
+ * count is written to *n_workers_out (device int32).
+ *
+ * void_plan_segments cuts the tile stream into n_cta contiguous shares of (nearly) equal
+ * weight.  With split_rows = 0 share boundaries fall on tile-row boundaries; with
+ * split_rows = 1 a boundary may fall on a chunk boundary of the worker table inside a heavy
+ * row; with split_rows = 2 every worker of the table becomes a segment of its own.
+ * Output: segs (8 int32 each: row, n_chunk, t0, t1, nseg, slot0, my_idx, counter),
+ * cta_seg_ptr[n_cta+1], counts[4] = {n_segs, n_slots, n_counters, overflow flag}; segs needs
+ * void_plan_capacity(...) entries.
+ * ------------------------------------------------------------------------------------- */
+VOID_API int64_t void_streamk_table_capacity(int64_t nnz, int32_t nbr);
+/* chunk length ("target_work") of the table: void/stream_k.py:61-67; 0 when nnz == 0 */
+VOID_API int32_t void_streamk_target(int64_t nnz, int32_t n_workers_req, int32_t max_work);
+/* ws: caller scratch of (nbr + 1) int32 */
+VOID_API int void_streamk_table(const int32_t* row_ptr, int32_t nbr, int64_t nnz, int32_t n_workers_req,
+                       int32_t max_work, int32_t* worker_rows, int32_t* worker_block_start,
+                       int32_t* worker_block_end, uint8_t* worker_needs_atomic,
+                       int32_t* n_workers_out, int32_t* ws, void_stream_t stream);
+VOID_API int64_t void_plan_capacity(int64_t nnz, int32_t nbr, int32_t n_chunks, int32_t n_cta,
+                                    int32_t split_rows, int32_t chunk_tiles);
+VOID_API size_t void_plan_ws_bytes(int32_t nbr, int32_t n_cta);
+/* chunk_tiles: chunk length of the worker table (void_streamk_target), used when split_rows > 0.
+ * woff: (nbr + 1) workers-before-row prefix left in the ws of void_streamk_table, needed for
+ * split_rows = 2 only.  ws: device scratch of void_plan_ws_bytes(nbr, n_cta) bytes.          */
+VOID_API int void_plan_segments(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, int32_t n_cta,
+                                int32_t split_rows, int32_t chunk_tiles, const int32_t* woff,
+                                int32_t* segs, int64_t segs_capacity, int32_t* cta_seg_ptr,
+                                int32_t* counts, void* ws, size_t ws_bytes, void_stream_t stream);
+/* The same splitting arithmetic over HOST arrays, run as plain loops on the CPU.  It exists so
+ * that the splitter can be tested on machines without a GPU; the SpMM path never calls it.   */
+VOID_API int void_plan_segments_host(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks,
+                                     int32_t n_cta, int32_t split_rows, int32_t chunk_tiles,
+                                     const int32_t* woff, int32_t* segs, int64_t segs_capacity,
+                                     int32_t* cta_seg_ptr, int32_t* counts);
+
+/* ---------------------------------------------------------------------------------------
+ * SpMM  C = act(dequant(A_q . B_q) + bias).
+ * void_spmm_i8 replaces void_spmm_int8_kernel / void_spmm_int8, void/int_quant.py:435-612;
+ * void_spmm_f8 replaces void_spmm_fp8_kernel / void_spmm_fp8, void/fp8.py:577-742 (with B
+ * also E4M3 and a per-column scale of B in the epilogue); act/bias give the fused epilogue
+ * of void_spmm_activation_kernel, void/fusion.py:98-198, :38-43; a plan with split rows
+ * gives the load-balanced form of stream_k_spmm_kernel, void/stream_k.py:113-230, without
+ * its spin lock.
+ * ------------------------------------------------------------------------------------- */
+typedef struct void_spmm_args {
+  /* A, packed (see void_pack_tiles) */
+  const void* tiles;        /* nnz * 1024 bytes, 1024-byte aligned                       */
+  const int32_t* tile_cols; /* [nnz] block column of each packed tile                    */
+  const float* tile_scales; /* [nnz] tile scales in packed order (VOID_SCALE_PER_TILE)   */
+  const int32_t* row_ptr;   /* [nbr+1]                                                   */
+  const float* row_scale;   /* [nbr] mean tile scale per row (VOID_SCALE_ROW_MEAN)       */
+  int32_t nbr, nbc;
+  int64_t nnz;
+  /* B, row-major [K, N] 8-bit, ldb bytes between k rows (multiple of 16)                */
+  const void* b;
+  int64_t ldb;
+  int32_t K, N;
+  const float* col_scale; /* [N] per-column scale of B, or NULL                          */
+  float b_scale;          /* scalar scale of B (1.0 when col_scale carries it)           */
+  const float* bias;      /* [N] column bias added before the activation, or NULL        */
+  /* C, row-major [M, N], ldc elements between rows                                      */
+  void* out;
+  int64_t ldc;
+  int32_t M;
+  int32_t out_dtype; /* VOID_OUT_*  */
+  int32_t act;       /* VOID_ACT_*  */
+  int32_t scale_mode; /* VOID_SCALE_* */
+  /* optional raw accumulators, [nbr*32, N] int32 (INT8) or fp32 (FP8), ROW_MEAN mode    */
+  void* acc_out;
+  /* plan (see void_plan_segments); segs == NULL: one segment per (tile row, column chunk) */
+  const int32_t* segs;
+  const int32_t* cta_seg_ptr;
+  int32_t n_cta;             /* CTAs the plan was made for; 0 without a plan             */
+  void* partials;            /* n_slots * 32 * chunk_cols * 4 bytes, split rows only     */
+  int64_t partials_bytes;
+  int32_t* counters;         /* [n_counters] zero before the first use; left zero again  */
+  void* worker_partials;     /* optional [n_segs, 32, N] int32: every segment's own sum  */
+  /* device status word: 0, or a code written by a bounded wait that gave up             */
+  int32_t* status;
+  /* launch shape; 0 = library default                                                   */
+  int32_t panels_per_item; /* 128-column panels of B per work item: 1, 2 or 4            */
+  int32_t stages;          /* shared-memory ring depth                                   */
+  int32_t grid;            /* CTAs to launch without a plan                              */
+  int32_t reserved;
+} void_spmm_args;
+
+VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);
+VOID_API int void_spmm_f8(const void_spmm_args* args, void_stream_t stream);
+
+/* number of SMs of the current device (grid sizing on the host side) */
+VOID_API int void_device_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VOID_B200_H_ */

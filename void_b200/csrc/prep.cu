@@ -1,0 +1,418 @@
+// Preparation kernels of the SpMM path: tile index (row_ptr / block_indices), packing of the
+// Morton-ordered tiles into tile-row-major core-matrix order, the INT8 / FP8-E4M3 quantisers
+// for A tiles and for the columns of B, and the Stream-K worker table.  All of them are
+// bandwidth-bound elementwise or gather kernels; none waits on another CTA.
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/void_b200.h"
+
+namespace vb {
+
+static inline cudaStream_t as_stream(void_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+static inline int last_status() { return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA; }
+
+// Exclusive prefix sum of n int32 values by ONE block of 1024 threads; out[n] = total.
+// in and out may alias.
+__device__ void block_exclusive_scan(const int32_t* in, int32_t* out, int n) {
+  __shared__ int32_t part[1024];
+  const int tid = threadIdx.x;
+  const int per = (n + 1023) / 1024;
+  const int lo = tid * per < n ? tid * per : n;
+  const int hi = (lo + per) < n ? (lo + per) : n;
+  int32_t s = 0;
+  for (int i = lo; i < hi; ++i) s += in[i];
+  part[tid] = s;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int32_t v = (tid >= off) ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  int32_t run = part[tid] - s;  // exclusive prefix of this thread's chunk
+  for (int i = lo; i < hi; ++i) {
+    const int32_t v = in[i];
+    out[i] = run;
+    run += v;
+  }
+  if (tid == 1023) out[n] = part[1023];
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------ tile index
+__global__ void mark_tiles_kernel(const int32_t* __restrict__ brow, const int32_t* __restrict__ bcol, int64_t nnz,
+                                  int wpr, uint32_t* __restrict__ bitmap) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nnz) return;
+  const int r = brow[i], c = bcol[i];
+  atomicOr(bitmap + (size_t)r * wpr + (c >> 5), 1u << (c & 31));
+}
+
+__global__ void count_rows_kernel(const uint32_t* __restrict__ bitmap, int nbr, int wpr, int32_t* __restrict__ counts) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= nbr) return;
+  int c = 0;
+  for (int w = lane; w < wpr; w += 32) c += __popc(bitmap[(size_t)warp * wpr + w]);
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if (lane == 0) counts[warp] = c;
+}
+
+__global__ void __launch_bounds__(1024) scan_rows_kernel(const int32_t* counts, int32_t* row_ptr, int nbr) {
+  block_exclusive_scan(counts, row_ptr, nbr);
+}
+
+__global__ void rank_tiles_kernel(const int32_t* __restrict__ brow, const int32_t* __restrict__ bcol, int64_t nnz,
+                                  int wpr, const uint32_t* __restrict__ bitmap, const int32_t* __restrict__ row_ptr,
+                                  int32_t* __restrict__ block_indices) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nnz) return;
+  const int r = brow[i], c = bcol[i];
+  const uint32_t* row = bitmap + (size_t)r * wpr;
+  int rank = 0;
+  for (int w = 0; w < (c >> 5); ++w) rank += __popc(row[w]);
+  rank += __popc(row[c >> 5] & ((1u << (c & 31)) - 1u));
+  block_indices[row_ptr[r] + rank] = (int32_t)i;
+}
+
+// ------------------------------------------------------------------------------ pack
+// One thread per 16-byte chunk of the packed tile.  Packed chunk q of a tile holds bytes
+// [c16*16, c16*16+16) of tile row r with  q = (r/8)*16 + c16*8 + (r%8): four groups of eight
+// rows, each group stored as two 8x16-byte core matrices (k bytes 0..15, then 16..31).
+__global__ void pack_tiles_kernel(const uint4* __restrict__ values, const int32_t* __restrict__ block_indices,
+                                  int64_t nnz, uint4* __restrict__ packed) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= nnz * 64) return;
+  const int64_t j = g >> 6;
+  const int q = (int)(g & 63);
+  const int r = (q >> 4) * 8 + (q & 7);
+  const int c16 = (q >> 3) & 1;
+  const int64_t src_tile = block_indices[j];
+  packed[g] = values[src_tile * 64 + r * 2 + c16];
+}
+
+__global__ void gather_tile_meta_kernel(const int32_t* __restrict__ bcol, const float* __restrict__ scales,
+                                        int64_t n_scales, const int32_t* __restrict__ block_indices, int64_t nnz,
+                                        int32_t* __restrict__ tile_cols, float* __restrict__ tile_scales) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= nnz) return;
+  const int64_t src = block_indices[j];
+  tile_cols[j] = bcol[src];
+  if (tile_scales != nullptr) tile_scales[j] = (scales == nullptr) ? 1.0f : (n_scales == 1 ? scales[0] : scales[src]);
+}
+
+// mean of the row's tile scales, added one by one in row order like the reference's loop
+__global__ void row_scale_kernel(const int32_t* __restrict__ row_ptr, const float* __restrict__ tile_scales, int nbr,
+                                 float* __restrict__ row_scale) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= nbr) return;
+  const int t0 = row_ptr[r], t1 = row_ptr[r + 1];
+  float s = 0.0f;
+  for (int t = t0; t < t1; ++t) s = __fadd_rn(s, tile_scales[t]);
+  row_scale[r] = (t1 > t0) ? __fdiv_rn(s, (float)(t1 - t0)) : 0.0f;
+}
+
+// ------------------------------------------------------------------------------ quantisers
+__device__ __forceinline__ float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int8_t quant_i8(float x, float scale) {
+  float q = rintf(__fdiv_rn(x, scale));
+  q = fminf(fmaxf(q, -128.0f), 127.0f);
+  return (int8_t)(int)q;
+}
+__device__ __forceinline__ uint8_t quant_e4m3(float x, float scale_inv) {
+  float s = __fmul_rn(x, scale_inv);
+  s = fminf(fmaxf(s, -448.0f), 448.0f);
+  return (uint8_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+}
+
+// one warp per tile: 1024 fp32 values, 32 per lane
+__global__ void quant_i8_tiles_kernel(const float4* __restrict__ values, int64_t nnz, int8_t* __restrict__ q,
+                                      float* __restrict__ scales) {
+  const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (tile >= nnz) return;
+  const float4* src = values + tile * 256;
+  float4 v[8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] = src[i * 32 + lane];
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+  }
+  amax = warp_max(amax);
+  const float scale = fmaxf(__fdiv_rn(amax, 128.0f), 1e-8f);
+  if (lane == 0) scales[tile] = scale;
+  char4* dst = reinterpret_cast<char4*>(q) + tile * 256;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    char4 o;
+    o.x = quant_i8(v[i].x, scale); o.y = quant_i8(v[i].y, scale);
+    o.z = quant_i8(v[i].z, scale); o.w = quant_i8(v[i].w, scale);
+    dst[i * 32 + lane] = o;
+  }
+}
+
+__global__ void quant_fp8_tiles_kernel(const float4* __restrict__ values, int64_t nnz, uint8_t* __restrict__ q,
+                                       float* __restrict__ scale_out, float* __restrict__ scale_inv_out,
+                                       float* __restrict__ amax_out) {
+  const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (tile >= nnz) return;
+  const float4* src = values + tile * 256;
+  float4 v[8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] = src[i * 32 + lane];
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+  }
+  amax = warp_max(amax);
+  const float scale = fmaxf(__fdiv_rn(amax, 448.0f), 1e-12f);
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (lane == 0) {
+    scale_out[tile] = scale;
+    if (scale_inv_out != nullptr) scale_inv_out[tile] = inv;
+    if (amax_out != nullptr) amax_out[tile] = amax;
+  }
+  uchar4* dst = reinterpret_cast<uchar4*>(q) + tile * 256;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uchar4 o;
+    o.x = quant_e4m3(v[i].x, inv); o.y = quant_e4m3(v[i].y, inv);
+    o.z = quant_e4m3(v[i].z, inv); o.w = quant_e4m3(v[i].w, inv);
+    dst[i * 32 + lane] = o;
+  }
+}
+
+// column absmax of a row-major [K, N] matrix: block = 128 columns x a slab of k rows
+constexpr int kColBlock = 128;
+constexpr int kRowSlab = 256;
+__global__ void col_amax_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, float* __restrict__ amax) {
+  const int n = blockIdx.x * kColBlock + threadIdx.x;
+  if (n >= N) return;
+  const int k0 = blockIdx.y * kRowSlab;
+  const int k1 = (k0 + kRowSlab) < K ? (k0 + kRowSlab) : K;
+  float m = 0.0f;
+  for (int k = k0; k < k1; ++k) m = fmaxf(m, fabsf(b[(size_t)k * ldb + n]));
+  // non-negative floats order like their bit patterns
+  atomicMax(reinterpret_cast<int*>(amax) + n, __float_as_int(m));
+}
+__global__ void col_scale_kernel(float* __restrict__ scale, float* __restrict__ scale_inv, int N, int kind) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float amax = scale[n];
+  float s;
+  if (kind == VOID_KIND_I8) s = fmaxf(__fdiv_rn(amax, 128.0f), 1e-8f);
+  else s = fmaxf(__fdiv_rn(amax, 448.0f), 1e-12f);
+  scale[n] = s;
+  if (scale_inv != nullptr) scale_inv[n] = __fdiv_rn(1.0f, s);
+}
+__global__ void quant_cols_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, int kind,
+                                  uint8_t* __restrict__ q, int64_t ldq, const float* __restrict__ scale) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (n >= ldq) return;
+  uint8_t o = 0;
+  if (n < N) {
+    const float x = b[(size_t)k * ldb + n];
+    const float s = scale[n];
+    if (kind == VOID_KIND_I8) o = (uint8_t)quant_i8(x, s);
+    else o = quant_e4m3(x, __fdiv_rn(1.0f, s));
+  }
+  q[(size_t)k * ldq + n] = o;
+}
+
+// ------------------------------------------------------------------------------ Stream-K table
+__global__ void __launch_bounds__(1024) streamk_offsets_kernel(const int32_t* __restrict__ row_ptr, int nbr,
+                                                               int target, int32_t* __restrict__ woff,
+                                                               int32_t* __restrict__ n_workers_out) {
+  // woff[r] = number of chunks of row r, then scanned in place
+  for (int r = threadIdx.x; r < nbr; r += blockDim.x) {
+    const int cnt = row_ptr[r + 1] - row_ptr[r];
+    woff[r] = (cnt + target - 1) / target;
+  }
+  __syncthreads();
+  block_exclusive_scan(woff, woff, nbr);
+  if (threadIdx.x == 0) *n_workers_out = woff[nbr];
+}
+__global__ void streamk_fill_kernel(const int32_t* __restrict__ row_ptr, int nbr, int target,
+                                    const int32_t* __restrict__ woff, int32_t* __restrict__ w_rows,
+                                    int32_t* __restrict__ w_start, int32_t* __restrict__ w_end,
+                                    uint8_t* __restrict__ w_atomic) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= nbr) return;
+  const int rs = row_ptr[r], re = row_ptr[r + 1];
+  const int chunks = woff[r + 1] - woff[r];
+  int w = woff[r];
+  for (int pos = rs; pos < re; pos += target, ++w) {
+    const int e = (pos + target) < re ? (pos + target) : re;
+    w_rows[w] = r;
+    w_start[w] = pos;
+    w_end[w] = e;
+    w_atomic[w] = chunks > 1 ? 1 : 0;
+  }
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+extern "C" {
+
+const char* void_strerror(int status) {
+  switch (status) {
+    case VOID_OK: return "ok";
+    case VOID_ERR_BAD_ARG: return "bad argument (null pointer, negative size or unknown enum value)";
+    case VOID_ERR_ALIGN: return "pointer or leading dimension breaks an alignment rule";
+    case VOID_ERR_SHAPE: return "unsupported shape";
+    case VOID_ERR_ARCH: return "current device is not an sm_100 (B200) GPU";
+    case VOID_ERR_CUDA: return "a CUDA runtime or driver call failed";
+    case VOID_ERR_WORKSPACE: return "workspace too small";
+    case VOID_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case VOID_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    default: return "unknown status";
+  }
+}
+
+int void_b200_abi_version(void) { return VOID_B200_ABI_VERSION; }
+
+size_t void_tile_index_ws_bytes(int32_t nbr, int32_t nbc) {
+  if (nbr <= 0 || nbc <= 0) return 16;
+  const size_t wpr = ((size_t)nbc + 31) / 32;
+  return (size_t)nbr * wpr * 4 + (size_t)nbr * 4 + 16;
+}
+
+int void_build_tile_index(const int32_t* block_rows, const int32_t* block_cols, int64_t nnz, int32_t nbr,
+                          int32_t nbc, int32_t* row_ptr, int32_t* block_indices, void* ws, size_t ws_bytes,
+                          void_stream_t stream) {
+  if (nnz < 0 || nbr < 0 || nbc < 0 || row_ptr == nullptr) return VOID_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  if (nbr == 0) return cudaMemsetAsync(row_ptr, 0, 4, st) == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
+  if (nnz > 0 && (block_rows == nullptr || block_cols == nullptr || block_indices == nullptr)) return VOID_ERR_BAD_ARG;
+  if (nnz > 0x7fffffffLL) return VOID_ERR_TOO_LARGE;
+  if (ws == nullptr || ws_bytes < void_tile_index_ws_bytes(nbr, nbc)) return VOID_ERR_WORKSPACE;
+  const int wpr = (nbc + 31) / 32;
+  uint32_t* bitmap = reinterpret_cast<uint32_t*>(ws);
+  int32_t* counts = reinterpret_cast<int32_t*>(bitmap + (size_t)nbr * wpr);
+  if (cudaMemsetAsync(bitmap, 0, (size_t)nbr * wpr * 4, st) != cudaSuccess) return VOID_ERR_CUDA;
+  const int tb = 256;
+  if (nnz > 0) mark_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, wpr, bitmap);
+  count_rows_kernel<<<(unsigned)(((int64_t)nbr * 32 + tb - 1) / tb), tb, 0, st>>>(bitmap, nbr, wpr, counts);
+  scan_rows_kernel<<<1, 1024, 0, st>>>(counts, row_ptr, nbr);
+  if (nnz > 0)
+    rank_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, wpr, bitmap, row_ptr,
+                                                                     block_indices);
+  return last_status();
+}
+
+int void_pack_tiles(const void* values, const float* scales, int64_t n_scales, const int32_t* block_cols,
+                    const int32_t* block_indices, const int32_t* row_ptr, int64_t nnz, int32_t nbr, void* packed,
+                    int32_t* tile_cols, float* tile_scales, float* row_scale, void_stream_t stream) {
+  if (nnz < 0 || nbr < 0) return VOID_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  const int tb = 256;
+  if (nnz > 0) {
+    if (values == nullptr || block_cols == nullptr || block_indices == nullptr || packed == nullptr ||
+        tile_cols == nullptr)
+      return VOID_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(values) & 15u) != 0 || (reinterpret_cast<uintptr_t>(packed) & 1023u) != 0)
+      return VOID_ERR_ALIGN;
+    if (scales != nullptr && n_scales != 1 && n_scales != nnz) return VOID_ERR_BAD_ARG;
+    pack_tiles_kernel<<<(unsigned)((nnz * 64 + tb - 1) / tb), tb, 0, st>>>(
+        reinterpret_cast<const uint4*>(values), block_indices, nnz, reinterpret_cast<uint4*>(packed));
+    gather_tile_meta_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_cols, scales, n_scales, block_indices,
+                                                                           nnz, tile_cols, tile_scales);
+  }
+  if (row_scale != nullptr && nbr > 0) {
+    if (row_ptr == nullptr || (nnz > 0 && tile_scales == nullptr)) return VOID_ERR_BAD_ARG;
+    row_scale_kernel<<<(nbr + tb - 1) / tb, tb, 0, st>>>(row_ptr, tile_scales, nbr, row_scale);
+  }
+  return last_status();
+}
+
+int void_quant_i8_tiles(const float* values, int64_t nnz, int8_t* q, float* scales, void_stream_t stream) {
+  if (nnz < 0) return VOID_ERR_BAD_ARG;
+  if (nnz == 0) return VOID_OK;
+  if (values == nullptr || q == nullptr || scales == nullptr) return VOID_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(values) & 15u) != 0 || (reinterpret_cast<uintptr_t>(q) & 3u) != 0) return VOID_ERR_ALIGN;
+  const int tb = 256;
+  quant_i8_tiles_kernel<<<(unsigned)((nnz * 32 + tb - 1) / tb), tb, 0, as_stream(stream)>>>(
+      reinterpret_cast<const float4*>(values), nnz, q, scales);
+  return last_status();
+}
+
+int void_quant_fp8_tiles(const float* values, int64_t nnz, uint8_t* q, float* scale, float* scale_inv, float* amax,
+                         void_stream_t stream) {
+  if (nnz < 0) return VOID_ERR_BAD_ARG;
+  if (nnz == 0) return VOID_OK;
+  if (values == nullptr || q == nullptr || scale == nullptr) return VOID_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(values) & 15u) != 0 || (reinterpret_cast<uintptr_t>(q) & 3u) != 0) return VOID_ERR_ALIGN;
+  const int tb = 256;
+  quant_fp8_tiles_kernel<<<(unsigned)((nnz * 32 + tb - 1) / tb), tb, 0, as_stream(stream)>>>(
+      reinterpret_cast<const float4*>(values), nnz, q, scale, scale_inv, amax);
+  return last_status();
+}
+
+int void_quant_cols(const float* b, int64_t ldb, int32_t K, int32_t N, int32_t kind, void* q, int64_t ldq,
+                    float* col_scale, float* col_scale_inv, void_stream_t stream) {
+  if (K < 0 || N < 0 || (kind != VOID_KIND_I8 && kind != VOID_KIND_F8E4M3)) return VOID_ERR_BAD_ARG;
+  if (K == 0 || N == 0) return VOID_OK;
+  if (b == nullptr || q == nullptr || col_scale == nullptr) return VOID_ERR_BAD_ARG;
+  if (ldb < N || ldq < N) return VOID_ERR_SHAPE;
+  if (K > 65535 * kRowSlab) return VOID_ERR_TOO_LARGE;
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(col_scale, 0, (size_t)N * 4, st) != cudaSuccess) return VOID_ERR_CUDA;
+  dim3 g1((N + kColBlock - 1) / kColBlock, (K + kRowSlab - 1) / kRowSlab);
+  col_amax_kernel<<<g1, kColBlock, 0, st>>>(b, ldb, K, N, col_scale);
+  col_scale_kernel<<<(N + 255) / 256, 256, 0, st>>>(col_scale, col_scale_inv, N, kind);
+  if (K > 65535) {
+    // blockIdx.y is limited to 65535: quantise in slabs of rows
+    for (int k0 = 0; k0 < K; k0 += 65535) {
+      const int kk = (K - k0) < 65535 ? (K - k0) : 65535;
+      dim3 g2((unsigned)((ldq + 255) / 256), kk);
+      quant_cols_kernel<<<g2, 256, 0, st>>>(b + (size_t)k0 * ldb, ldb, kk, N, kind,
+                                            reinterpret_cast<uint8_t*>(q) + (size_t)k0 * ldq, ldq, col_scale);
+    }
+  } else {
+    dim3 g2((unsigned)((ldq + 255) / 256), K);
+    quant_cols_kernel<<<g2, 256, 0, st>>>(b, ldb, K, N, kind, reinterpret_cast<uint8_t*>(q), ldq, col_scale);
+  }
+  return last_status();
+}
+
+int64_t void_streamk_table_capacity(int64_t nnz, int32_t nbr) {
+  (void)nbr;
+  return nnz > 0 ? nnz : 1;
+}
+
+int32_t void_streamk_target(int64_t nnz, int32_t n_workers_req, int32_t max_work) {
+  // target_work of compute_stream_k_workload, void/stream_k.py:61-67
+  if (nnz <= 0) return 0;
+  int64_t n_workers = n_workers_req > 0 ? n_workers_req : (nnz < 1024 ? nnz : 1024);
+  int64_t target = (nnz + n_workers - 1) / n_workers;
+  if (target > max_work) target = max_work;
+  return (int32_t)target;
+}
+
+int void_streamk_table(const int32_t* row_ptr, int32_t nbr, int64_t nnz, int32_t n_workers_req, int32_t max_work,
+                       int32_t* worker_rows, int32_t* worker_block_start, int32_t* worker_block_end,
+                       uint8_t* worker_needs_atomic, int32_t* n_workers_out, int32_t* ws, void_stream_t stream) {
+  if (row_ptr == nullptr || nbr <= 0 || nnz <= 0 || max_work <= 0) return VOID_ERR_BAD_ARG;
+  if (worker_rows == nullptr || worker_block_start == nullptr || worker_block_end == nullptr ||
+      worker_needs_atomic == nullptr || n_workers_out == nullptr || ws == nullptr)
+    return VOID_ERR_BAD_ARG;
+  const int target = void_streamk_target(nnz, n_workers_req, max_work);
+  if (target <= 0) return VOID_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  streamk_offsets_kernel<<<1, 1024, 0, st>>>(row_ptr, nbr, target, ws, n_workers_out);
+  streamk_fill_kernel<<<(nbr + 255) / 256, 256, 0, st>>>(row_ptr, nbr, target, ws, worker_rows, worker_block_start,
+                                                        worker_block_end, worker_needs_atomic);
+  return last_status();
+}
+
+}  // extern "C"
