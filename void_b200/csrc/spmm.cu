@@ -692,18 +692,19 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.n_items = a->nbr * n_chunks;
 
   // operand descriptors (see the header comment for the two shared-memory layouts)
-  uint32_t tile_lbo = 128, tile_sbo = 256;
+  uint32_t tile_lbo = 128, tile_sbo = 256, tile_layout = kLayoutNone;
   const int variant = desc_variant();
   if (variant & 1) { tile_lbo = 256; tile_sbo = 128; }
-  uint32_t panel_lbo = (variant & 2) ? 1024u : 0u;
-  p.desc_hi_b = smem_desc_hi(tile_lbo, tile_sbo, kLayoutNone);
-  p.desc_hi_a = smem_desc_hi(panel_lbo, 1024, kLayoutSw128);
+  if (variant & 2) { tile_lbo = 16; tile_sbo = 256; tile_layout = kLayoutSw32; }
+  p.desc_hi_b = smem_desc_hi(tile_lbo, tile_sbo, tile_layout);
+  // one 128-byte swizzle atom along n, four 8-row groups along k, 1024 bytes apart
+  p.desc_hi_a = smem_desc_hi(1024, 1024, kLayoutSw128);
   if (kind == VOID_KIND_I8) p.idesc = instr_desc(/*c s32*/ 2, /*a s8*/ 1, /*b s8*/ 1, /*a MN*/ 1, /*b K*/ 0, 128, 32);
   else p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, 1, 0, 128, 32);
 
   int grid;
   if (a->segs != nullptr) {
-    if (a->cta_seg_ptr == nullptr || a->n_cta <= 0) return VOID_ERR_BAD_ARG;
+    if (a->cta_seg_ptr == nullptr || a->n_cta <= 0 || a->panels_per_item == 0) return VOID_ERR_BAD_ARG;
     if (drain) return VOID_ERR_BAD_ARG;  // split rows are finished by the row-accumulate kernel only
     grid = a->n_cta;
   } else {
