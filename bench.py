@@ -1,0 +1,458 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized block-sparse SpMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path - one SpMM launch over one
+batch of synthetic input.  Workloads:
+
+  headline (default)  4096 x 4096, 32x32 tiles, uniform random block mask at 90 % block sparsity,
+                      A INT8 per block, B 4096 x 512 INT8 per column, int32 accumulate, fp16 out.
+                      With N GPUs the global A is (4096*N) x 4096 sharded ROW_WISE - 4096 rows per
+                      rank, B replicated by one NCCL broadcast at set-up, no collective in the step
+                      (weak scaling: work per GPU is fixed).
+  fp8                 same shape, A and B in FP8 E4M3 (per-block / per-column scales), fp32 accumulate.
+  powerlaw            16384 x 16384, Zipf(1.5) tile-row lengths, N = 256, INT8, Stream-K + GELU, bf16 out.
+  sharded             65536 x 65536 at 95 %, N = 1024, INT8, ROW_WISE shards over the ranks (strong
+                      scaling: the total work is fixed).
+
+value  = whole-job TOPS over the nonzero tiles (2*nnz*32*32*N per step) with inputs resident in HBM.
+e2e    = the same metric through the public operator with HOST buffers: every step copies that step's
+         B (and its column scales) from pinned host memory to the device, runs the operator and
+         copies C back.  A, the sparse operand, is resident like a weight.
+L2     = the step rotates over enough distinct copies of (A, B, C) to exceed the 126 MB L2, so the
+         kernel reads its inputs from HBM ("l2": "rotating_inputs" in config).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "block_sparse_spmm_tops_nonzero_tiles"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded"])
+    ap.add_argument("--sparsity", type=float, default=0.9)
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--copies", type=int, default=0, help="distinct input copies to rotate over (0 = enough for L2)")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons of one GPU through NVML while the benchmark runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.samples, self.stop_flag, self.window = [], False, [None, None]
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        t0, t1 = self.window
+        inside = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1]
+        use = inside if inside else self.samples
+        mhz = sorted(s[1] for s in use)
+        bits = 0
+        for s in use:
+            bits |= s[2]
+        names = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        reasons = [n for b, n in names.items() if bits & b and n != "gpu_idle"]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(use), "samples_in_timed_region": len(inside)}
+
+
+# ----------------------------------------------------------------------------------------------
+def cpu_reference_arm(args, rank, world):
+    """The reference has no compiled CPU kernel; its arithmetic for this path, restated on the CPU
+    (oracle/void_oracle.py: int32 tile-row products through float64 BLAS, mean-scale epilogue), is
+    timed on the host cores.  Rank 0 only."""
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import void_oracle as vo
+    cfg, run, cores = cpu_workload(args, np, torch, vo)
+    for _ in range(min(args.warmup, 1)):
+        run()
+    t0 = time.perf_counter()
+    n = 0
+    budget = 120.0
+    while n < args.steps and (time.perf_counter() - t0) < budget:
+        run()
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    tops = cfg["ops"] / dt / 1e12
+    line = {
+        "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus, "steps": n, "warmup": min(args.warmup, 1),
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": cfg["dtype"], "data": "synthetic", "impl": "reference", "config": cfg["config"],
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+                         "sample": "whole %s workload per step, %d steps" % (cfg["config"]["workload"], n)},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def cpu_workload(args, np, torch, vo):
+    """Host copy of the N=1 workload + a closure that runs the oracle on it once."""
+    from void_b200 import workloads
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if args.workload == "powerlaw":
+        mask, N, name = workloads.zipf_mask(512, 512, 1.5, 512, 15.36, 0), 256, "zipf16384_n256"
+    else:
+        mask, N, name = workloads.uniform_mask(128, 128, args.sparsity, 0), 512, "uniform4096_bs%02d_n512" % round(args.sparsity * 100)
+    rows, cols = np.nonzero(mask)
+    order = np.argsort(vo.morton_encode_batch(rows, cols))
+    rows, cols = rows[order].astype(np.int32), cols[order].astype(np.int32)
+    g = torch.Generator().manual_seed(0)
+    vals = torch.randn(len(rows), 32, 32, generator=g).numpy()
+    b = torch.randn(mask.shape[1] * 32, N, generator=g).numpy()
+    shape = (mask.shape[0] * 32, mask.shape[1] * 32)
+    if args.workload == "fp8":
+        q, s, _, _ = vo.quantize_fp8_tiles(vals)
+        bq, bs, _ = vo.quantize_fp8_cols(b)
+        b_deq = vo.fp8_bytes_to_float(bq) * bs[None, :]
+        run = lambda: vo.spmm_fp8(q, s, rows, cols, shape, b_deq).astype(np.float16)
+        dtype = "f8e4m3"
+    else:
+        q, s = vo.quantize_int8_tiles(vals)
+        bq, bs = vo.quantize_int8_cols(b)
+        if args.workload == "powerlaw":
+            run = lambda: vo.gelu_tanh_sigmoid(vo.spmm_int8(q, s, rows, cols, shape, bq, col_scale=bs))
+        else:
+            run = lambda: vo.spmm_int8(q, s, rows, cols, shape, bq, col_scale=bs).astype(np.float16)
+        dtype = "i8"
+    cfg = {"ops": workloads.spmm_ops(len(rows), N), "dtype": dtype,
+           "config": {"workload": name, "M": shape[0], "K": shape[1], "N": N, "tile": 32, "nnz_tiles": int(len(rows)),
+                      "block_sparsity": 1.0 - len(rows) / mask.size}}
+    return cfg, run, cores
+
+
+# ----------------------------------------------------------------------------------------------
+def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
+    """Per-rank operands: a list of (A quantised, B 8-bit, B scales, out) copies to rotate over."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sets = []
+    if args.workload == "sharded":
+        shard, (start, end), nnz_global = workloads.sharded_int8(world_size=world, rank=rank, device=dev)
+        g = torch.Generator(device="cpu").manual_seed(0)
+        N, K = 1024, 65536
+        if rank == 0:
+            b = torch.randn(K, N, generator=g).to(dev)
+            bq, bs = void.quantize_cols_int8(b)
+            bq = bq.contiguous()
+            del b
+        else:
+            bq = torch.empty(K, N, dtype=torch.int8, device=dev)
+            bs = torch.empty(N, dtype=torch.float32, device=dev)
+        out = torch.empty(shard.shape[0], N, dtype=torch.float16, device=dev)
+        sets.append([shard, bq, bs, out])
+        info = {"name": "uniform65536_bs95_n1024_rowshards", "M": 65536, "K": K, "N": N, "out": torch.float16,
+                "kind": "i8", "nnz_local": shard.n_blocks, "rows_local": shard.shape[0], "nbr_local": shard.block_grid[0]}
+        return sets, info
+    if args.workload == "powerlaw":
+        make = lambda seed: workloads.power_law(seed=seed, device=dev)
+        N, out_dtype, kind = 256, torch.bfloat16, "i8"
+    else:
+        make = lambda seed: workloads.headline(args.sparsity, seed=seed, device=dev)
+        N, out_dtype, kind = 512, torch.float16, ("f8e4m3" if args.workload == "fp8" else "i8")
+    # every rank owns different tile rows of the global A (its own seeds); with several ranks the B
+    # quantised here is overwritten by rank 0's B in the broadcast that follows
+    n_copies = None
+    i = 0
+    while n_copies is None or i < n_copies:
+        w = make(seed=1000 * rank + i)
+        if kind == "i8":
+            a = void.quantize_void_tensor(w.a)
+            bq, bs = void.quantize_cols_int8(w.b)
+        else:
+            a = void.void_tensor_to_fp8(w.a)
+            bq, bs, _ = void.quantize_cols_fp8(w.b)
+        a.packed()
+        out = torch.empty(w.shape[0], N, dtype=out_dtype, device=dev)
+        sets.append([a, bq.contiguous(), bs, out])
+        if n_copies is None:
+            per_copy = workloads.algorithmic_bytes(w.nnz, w.shape[0] // 32, w.shape[1], N, w.shape[0], out.element_size())
+            n_copies = copies_hint if copies_hint > 0 else max(2, -(-2 * L2_BYTES // per_copy))
+        del w
+        i += 1
+    info = {"name": None, "N": N, "out": out_dtype, "kind": kind}
+    return sets, info
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        cpu_reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import void_b200 as void
+    from void_b200 import _lib, _spmm, workloads, stream_k
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (this path has no CPU implementation; see --impl reference)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.gpus != world and rank == 0:
+        print("bench.py: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (args.gpus, world), file=sys.stderr)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    sets, info = build_rank_inputs(args, rank, world, torch, void, workloads, args.copies)
+    # replicate B: one broadcast per copy from rank 0 over NCCL (set-up, timed separately)
+    bcast_ms = None
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in sets:
+            void.broadcast_b(s[1], src=0, scales=s[2])
+        e1.record()
+        torch.cuda.synchronize()
+        bcast_ms = e0.elapsed_time(e1) / len(sets)
+
+    kind = info["kind"]
+    is_powerlaw = args.workload == "powerlaw"
+
+    def step(i):
+        a, bq, bs, out = sets[i % len(sets)]
+        if is_powerlaw:
+            void.void_spmm_stream_k(a, bq, b_scale=bs, out=out, activation=_lib.ACT_GELU)
+        elif kind == "i8":
+            void.void_spmm_int8(a, bq, bs, out)
+        else:
+            void.void_spmm_fp8(a, bq, out.dtype, b_scale=bs, out=out)
+
+    # per-step work of this rank
+    nnz_local = [s[0].n_blocks for s in sets]
+    N = info["N"]
+    ops_per_step_local = float(np.mean([workloads.spmm_ops(n, N) for n in nnz_local]))
+    a0 = sets[0][0]
+    M_local, K = a0.shape
+    bytes_per_step = float(np.mean([workloads.algorithmic_bytes(n, a0.block_grid[0], K, N, M_local,
+                                                                sets[0][3].element_size()) for n in nnz_local]))
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    _lib.check_device_status(dev)
+
+    # the K timed steps: replayed CUDA graphs of up to 256 steps each, so that the GPU is not
+    # waiting for the Python launch path between kernels
+    K_steps = args.steps
+    stream = torch.cuda.Stream(device=dev)
+    graphs = []
+    if not args.no_graph:
+        glen = min(K_steps, 256)
+        while glen > 1 and glen % len(sets) != 0 and glen > len(sets):
+            glen -= 1
+        with torch.cuda.stream(stream):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(glen):
+                    step(i)
+            rem = K_steps % glen
+            g_rem = None
+            if rem:
+                g_rem = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_rem, stream=stream):
+                    for i in range(rem):
+                        step(i)
+        graphs = [(g, K_steps // glen), (g_rem, 1 if rem else 0)]
+        with torch.cuda.stream(stream):
+            g.replay()
+        torch.cuda.synchronize()
+
+    def run_timed():
+        with torch.cuda.stream(stream):
+            if graphs:
+                for gr, reps in graphs:
+                    for _ in range(reps):
+                        gr.replay()
+            else:
+                for i in range(K_steps):
+                    step(i)
+
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.window[0] = time.perf_counter()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+    run_timed()
+    with torch.cuda.stream(stream):
+        e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.window[1] = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    ms_total = e0.elapsed_time(e1)
+    _lib.check_device_status(dev)
+
+    # ---- end to end through the public operator with host buffers
+    a_e, bq_e, bs_e, out_e = sets[0]
+    h_b = torch.empty(bq_e.shape, dtype=torch.uint8).pin_memory()
+    h_b.copy_(bq_e.view(torch.uint8).cpu())
+    h_s = bs_e.cpu().pin_memory()
+    h_c = torch.empty(out_e.shape, dtype=out_e.dtype).pin_memory()
+    d_b = torch.empty_like(bq_e)
+    d_s = torch.empty_like(bs_e)
+
+    def e2e_step():
+        d_b.view(torch.uint8).copy_(h_b, non_blocking=True)
+        d_s.copy_(h_s, non_blocking=True)
+        if is_powerlaw:
+            void.void_spmm_stream_k(a_e, d_b, b_scale=d_s, out=out_e, activation=_lib.ACT_GELU)
+        elif kind == "i8":
+            void.void_spmm_int8(a_e, d_b, d_s, out_e)
+        else:
+            void.void_spmm_fp8(a_e, d_b, out_e.dtype, b_scale=d_s, out=out_e)
+        h_c.copy_(out_e, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the caller owns the result on the host
+
+    e2e_steps = max(3, min(K_steps, 200))
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    e2e_ms = ev0.elapsed_time(ev1) / e2e_steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_ms = max(e2e_ms, e2e_wall_ms)
+
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+
+    # ---- aggregate over ranks: max time, summed work
+    t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    work = torch.tensor([ops_per_step_local, float(np.mean(nnz_local))], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms = (float(x) for x in t.tolist())
+    ops_per_step, nnz_total = (float(x) for x in work.tolist())
+
+    if rank == 0:
+        ms_per_step = ms_total / K_steps
+        value = ops_per_step / (ms_per_step * 1e-3) / 1e12
+        peaks = measured_peaks()
+        achieved = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+        ops_per_byte = ops_per_step_local / bytes_per_step
+        clocks = sampler.summary()
+        name = info["name"] or ("%s_x%d_rowshards" % (sets[0][0].__class__.__name__, world))
+        if args.workload in ("headline", "fp8"):
+            name = "uniform4096_bs%02d_n512%s" % (round(args.sparsity * 100), "" if world == 1 else "_x%d_rowshards" % world)
+        elif args.workload == "powerlaw":
+            name = "zipf16384_n256_streamk_gelu"
+        line = {
+            "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": K_steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
+            "dtype": kind, "data": "synthetic",
+            "config": {"workload": name, "M_per_gpu": M_local, "K": K, "N": N, "tile": 32,
+                       "nnz_tiles": nnz_total, "out_dtype": str(sets[0][3].dtype).replace("torch.", ""),
+                       "l2": "rotating_inputs", "input_copies": len(sets), "cuda_graph": not args.no_graph,
+                       "b_broadcast_ms": bcast_ms, "parallelism": "row_shards_x%d" % world},
+            "roofline": {"bound": "hbm" if ops_per_byte < 562 else "tensor", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": None, "peak_source": peaks["source"],
+                         "algorithmic_bytes_per_launch": bytes_per_step, "ops_per_byte": ops_per_byte,
+                         "kernel_us": ms_per_step * 1e3},
+            "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(h_b.numel() + h_s.numel() * 4),
+                    "d2h_bytes_per_step": int(h_c.numel() * h_c.element_size())},
+            "gpu_launches": K_steps,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1 and args.workload != "sharded":
+            from oracle import void_oracle as vo
+            cfg, run, cores = cpu_workload(args, np, torch, vo)
+            run()
+            t0 = time.perf_counter()
+            n = 0
+            while n < 200 and time.perf_counter() - t0 < 10.0:
+                run()
+                n += 1
+            dt = (time.perf_counter() - t0) / n
+            line["cpu_baseline"] = {"value": cfg["ops"] / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+                                    "sample": "whole workload x %d runs (%.1f s), float64-BLAS tile-row products" % (n, dt * n)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

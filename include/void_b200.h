@@ -112,6 +112,10 @@ VOID_API int void_quant_fp8_tiles(const float* values, int64_t nnz, uint8_t* q, 
 VOID_API int void_quant_cols(const float* b, int64_t ldb, int32_t K, int32_t N, int32_t kind, void* q,
                     int64_t ldq, float* col_scale, float* col_scale_inv,
                     void_stream_t stream);
+/* One symmetric INT8 scale for the whole [K, N] matrix (scale[0] = max(absmax/128, 1e-8)): the
+ * PER_TENSOR quantisation void_spmm_int8 applies to a floating-point B, void/int_quant.py:565-573. */
+VOID_API int void_quant_i8_tensor(const float* b, int64_t ldb, int32_t K, int32_t N, void* q, int64_t ldq,
+                                  float* scale, void_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Work plan.  A *segment* is a run of consecutive tiles of one tile row that one CTA

@@ -51,6 +51,7 @@ _PROTOTYPES = {
     "void_quant_i8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_fp8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "void_quant_cols": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp, c_vp]),
+    "void_quant_i8_tensor": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp]),
     "void_streamk_table_capacity": (c_i64, [c_i64, c_i32]),
     "void_streamk_target": (c_i32, [c_i64, c_i32, c_i32]),
     "void_streamk_table": (ctypes.c_int, [c_vp, c_i32, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),

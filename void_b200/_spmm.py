@@ -1,0 +1,226 @@
+"""Host side of the SpMM kernels: packed tile store, work plans and the launch itself.
+
+Every function here ends in a call of the C ABI (include/void_b200.h).  Nothing computes on the
+CPU; tensors that are not on a CUDA device are rejected.
+"""
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+TILE = 32
+PANEL = 128
+
+
+def _aligned_empty(nbytes: int, device, align: int = 1024) -> torch.Tensor:
+    """uint8 buffer whose data pointer is ``align``-byte aligned."""
+    raw = torch.empty(nbytes + align, dtype=torch.uint8, device=device)
+    off = (-raw.data_ptr()) % align
+    return raw[off:off + nbytes]
+
+
+@dataclass
+class PackedTiles:
+    """A in the layout the kernels stream: tiles in tile-row-major order, 1024 bytes each, already
+    in the tensor cores' core-matrix order, with per-tile column index and scale."""
+    tiles: torch.Tensor        # uint8 [nnz * 1024], 1024-byte aligned
+    tile_cols: torch.Tensor    # int32 [nnz]
+    tile_scales: torch.Tensor  # float32 [nnz]
+    row_ptr: torch.Tensor      # int32 [nbr + 1]
+    block_indices: torch.Tensor  # int32 [nnz]
+    row_scale: torch.Tensor    # float32 [nbr]
+    nbr: int
+    nbc: int
+    nnz: int
+    shape: tuple
+    kind: int                  # _lib.KIND_*
+    key: tuple = ()
+
+
+def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch.Tensor, block_cols: torch.Tensor,
+         shape, kind: int, row_ptr=None, block_indices=None) -> PackedTiles:
+    """Build the packed store of an 8-bit VOID tensor on its device (void_pack_tiles)."""
+    from .format import build_tile_index
+    _lib.require_cuda(values, block_rows, block_cols)
+    lib = _lib.load()
+    dev = values.device
+    M, K = shape
+    nbr, nbc = (M + TILE - 1) // TILE, (K + TILE - 1) // TILE
+    nnz = values.shape[0]
+    if values.dim() != 3 or values.shape[1] != TILE or values.shape[2] != TILE or values.element_size() != 1:
+        raise _lib.VoidB200Error("void_b200 kernels need 32x32 tiles of 8-bit elements, got %s %s"
+                                 % (tuple(values.shape), values.dtype))
+    with torch.cuda.device(dev):
+        if row_ptr is None or block_indices is None:
+            row_ptr, block_indices = build_tile_index(block_rows, block_cols, nbr, nbc)
+        vals = values.contiguous()
+        tiles = _aligned_empty(max(nnz, 1) * 1024, dev)
+        tile_cols = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)
+        tile_scales = torch.empty(max(nnz, 1), dtype=torch.float32, device=dev)
+        row_scale = torch.empty(max(nbr, 1), dtype=torch.float32, device=dev)
+        sc = None if scales is None else scales.contiguous().to(torch.float32).reshape(-1)
+        bc = block_cols.contiguous().to(torch.int32)
+        _lib.check(lib.void_pack_tiles(_lib.ptr(vals), _lib.ptr(sc), 0 if sc is None else sc.numel(), _lib.ptr(bc),
+                                       _lib.ptr(block_indices), _lib.ptr(row_ptr), nnz, nbr, _lib.ptr(tiles),
+                                       _lib.ptr(tile_cols), _lib.ptr(tile_scales), _lib.ptr(row_scale),
+                                       _lib.stream_ptr(dev)), "void_pack_tiles")
+    return PackedTiles(tiles, tile_cols, tile_scales, row_ptr, block_indices, row_scale, nbr, nbc, nnz,
+                       (M, K), kind)
+
+
+def cached_pack(owner, values, scales, block_rows, block_cols, shape, kind) -> PackedTiles:
+    """Packed store cached on the tensor object, rebuilt when its storage or contents change."""
+    key = (values.data_ptr(), values._version, None if scales is None else (scales.data_ptr(), scales._version),
+           block_rows.data_ptr(), block_cols.data_ptr(), str(values.device), tuple(shape))
+    p = getattr(owner, "_packed_cache", None)
+    if p is None or p.key != key:
+        p = pack(values, scales, block_rows, block_cols, shape, kind)
+        p.key = key
+        owner._packed_cache = p
+        owner._plan_cache = {}
+    return p
+
+
+@dataclass
+class Plan:
+    """Work plan of void_plan_segments for one (packed tensor, column chunking, CTA count)."""
+    segs: torch.Tensor
+    cta_seg_ptr: torch.Tensor
+    n_cta: int
+    np: int
+    n_chunks: int
+    n_segs: int
+    n_slots: int
+    n_counters: int
+    partials: Optional[torch.Tensor]
+    counters: torch.Tensor
+    mode: int
+    chunk_tiles: int
+
+
+def sm_count(device) -> int:
+    with torch.cuda.device(device):
+        return _lib.load().void_device_sm_count()
+
+
+def streamk_table(row_ptr: torch.Tensor, nbr: int, nnz: int, n_workers: Optional[int], max_work: int):
+    """Worker table on the device (void_streamk_table).  Returns the four arrays trimmed to the
+    realised worker count, the per-row worker offsets and the chunk length."""
+    lib = _lib.load()
+    dev = row_ptr.device
+    req = -1 if n_workers is None else int(n_workers)
+    if nnz == 0 or (n_workers is not None and req <= 0):
+        raise ZeroDivisionError("integer division or modulo by zero")  # as void/stream_k.py:66
+    target = lib.void_streamk_target(nnz, req, max_work)
+    with torch.cuda.device(dev):
+        cap = lib.void_streamk_table_capacity(nnz, nbr)
+        rows = torch.empty(cap, dtype=torch.int32, device=dev)
+        start = torch.empty(cap, dtype=torch.int32, device=dev)
+        end = torch.empty(cap, dtype=torch.int32, device=dev)
+        atomic = torch.empty(cap, dtype=torch.uint8, device=dev)
+        n_out = torch.zeros(1, dtype=torch.int32, device=dev)
+        woff = torch.empty(nbr + 1, dtype=torch.int32, device=dev)
+        _lib.check(lib.void_streamk_table(_lib.ptr(row_ptr), nbr, nnz, req, max_work, _lib.ptr(rows), _lib.ptr(start),
+                                          _lib.ptr(end), _lib.ptr(atomic), _lib.ptr(n_out), _lib.ptr(woff),
+                                          _lib.stream_ptr(dev)), "void_streamk_table")
+        n = int(n_out.item())
+    return rows[:n], start[:n], end[:n], atomic[:n].to(torch.bool), woff, target
+
+
+def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chunk_tiles: int = 0,
+              woff: Optional[torch.Tensor] = None) -> Plan:
+    """Cut the tile stream of ``packed`` into ``n_cta`` shares on the device (void_plan_segments)."""
+    lib = _lib.load()
+    dev = packed.row_ptr.device
+    panels = (N + PANEL - 1) // PANEL
+    n_chunks = (panels + np_ - 1) // np_
+    with torch.cuda.device(dev):
+        cap = lib.void_plan_capacity(packed.nnz, packed.nbr, n_chunks, n_cta, mode, chunk_tiles)
+        segs = torch.empty(cap * 8, dtype=torch.int32, device=dev)
+        cta_seg_ptr = torch.empty(n_cta + 1, dtype=torch.int32, device=dev)
+        counts = torch.zeros(4, dtype=torch.int32, device=dev)
+        ws_bytes = lib.void_plan_ws_bytes(packed.nbr, n_cta)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(lib.void_plan_segments(_lib.ptr(packed.row_ptr), packed.nbr, n_chunks, n_cta, mode, chunk_tiles,
+                                          _lib.ptr(woff), _lib.ptr(segs), cap, _lib.ptr(cta_seg_ptr), _lib.ptr(counts),
+                                          _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev)), "void_plan_segments")
+        n_segs, n_slots, n_ctr, overflow = (int(x) for x in counts.tolist())
+        if overflow:
+            raise _lib.VoidB200Error("void_plan_segments: segment list overflow")
+        partials = None
+        if n_slots:
+            partials = torch.empty(n_slots * np_ * PANEL * TILE, dtype=torch.int32, device=dev)
+        counters = torch.zeros(max(n_ctr, 1), dtype=torch.int32, device=dev)
+    return Plan(segs, cta_seg_ptr, n_cta, np_, n_chunks, n_segs, n_slots, n_ctr, partials, counters, mode,
+                chunk_tiles)
+
+
+def prepare_b(b: torch.Tensor) -> torch.Tensor:
+    """B as the kernels need it: 8-bit, row-major, 16-byte aligned rows (the copy engine's rule)."""
+    if b.element_size() != 1:
+        raise _lib.VoidB200Error("B must be 8-bit (int8 / float8_e4m3fn), got %s" % b.dtype)
+    if b.stride(1) != 1 or b.stride(0) % 16 != 0 or b.data_ptr() % 16 != 0 or b.stride(0) < b.shape[1]:
+        K, N = b.shape
+        ld = (N + 15) // 16 * 16
+        padded = torch.zeros(K, ld, dtype=b.dtype, device=b.device)
+        padded[:, :N] = b
+        b = padded[:, :N]
+    return b
+
+
+def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode: int, col_scale=None,
+         b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
+         worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
+         grid: int = 0) -> torch.Tensor:
+    """One launch of void_spmm_i8 / void_spmm_f8 on the current stream of b's device."""
+    lib = _lib.load()
+    _lib.require_cuda(b, out, packed.tiles)
+    dev = b.device
+    M, K = packed.shape
+    N = b.shape[1]
+    if b.shape[0] != K:
+        raise _lib.VoidB200Error("shape mismatch: A is %s, B is %s" % (packed.shape, tuple(b.shape)))
+    if tuple(out.shape) != (M, N) or out.stride(1) != 1:
+        raise _lib.VoidB200Error("out must be a row-major [%d, %d] tensor" % (M, N))
+    if out.dtype not in _lib.OUT_DTYPE_CODE:
+        raise _lib.VoidB200Error("unsupported output dtype %s" % out.dtype)
+    b = prepare_b(b)
+    a = _lib.SpmmArgs()
+    a.tiles = packed.tiles.data_ptr()
+    a.tile_cols = packed.tile_cols.data_ptr()
+    a.tile_scales = packed.tile_scales.data_ptr()
+    a.row_ptr = packed.row_ptr.data_ptr()
+    a.row_scale = packed.row_scale.data_ptr() if (use_row_scale and scale_mode == _lib.SCALE_ROW_MEAN) else None
+    a.nbr, a.nbc, a.nnz = packed.nbr, packed.nbc, packed.nnz
+    a.b, a.ldb, a.K, a.N = b.data_ptr(), b.stride(0), K, N
+    keep = [b]
+    if col_scale is not None:
+        col_scale = col_scale.to(device=dev, dtype=torch.float32).contiguous()
+        keep.append(col_scale)
+        a.col_scale = col_scale.data_ptr()
+    a.b_scale = float(b_scale)
+    if bias is not None:
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous()
+        keep.append(bias)
+        a.bias = bias.data_ptr()
+    a.out, a.ldc, a.M = out.data_ptr(), out.stride(0), M
+    a.out_dtype = _lib.OUT_DTYPE_CODE[out.dtype]
+    a.act = act
+    a.scale_mode = scale_mode
+    a.acc_out = None if acc_out is None else acc_out.data_ptr()
+    if plan is not None:
+        a.segs, a.cta_seg_ptr, a.n_cta = plan.segs.data_ptr(), plan.cta_seg_ptr.data_ptr(), plan.n_cta
+        if plan.partials is not None:
+            a.partials, a.partials_bytes = plan.partials.data_ptr(), plan.partials.numel() * 4
+        a.counters = plan.counters.data_ptr()
+        panels_per_item = plan.np
+    a.worker_partials = None if worker_partials is None else worker_partials.data_ptr()
+    a.status = _lib.status_word(dev).data_ptr()
+    a.panels_per_item, a.stages, a.grid = panels_per_item, stages, grid
+    fn = lib.void_spmm_i8 if packed.kind == _lib.KIND_I8 else lib.void_spmm_f8
+    with torch.cuda.device(dev):
+        _lib.check(fn(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm")
+    return out

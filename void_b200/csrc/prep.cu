@@ -226,18 +226,31 @@ __global__ void col_scale_kernel(float* __restrict__ scale, float* __restrict__ 
   if (scale_inv != nullptr) scale_inv[n] = __fdiv_rn(1.0f, s);
 }
 __global__ void quant_cols_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, int kind,
-                                  uint8_t* __restrict__ q, int64_t ldq, const float* __restrict__ scale) {
+                                  uint8_t* __restrict__ q, int64_t ldq, const float* __restrict__ scale,
+                                  int scale_stride) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   const int k = blockIdx.y;
   if (n >= ldq) return;
   uint8_t o = 0;
   if (n < N) {
     const float x = b[(size_t)k * ldb + n];
-    const float s = scale[n];
+    const float s = scale[(size_t)n * scale_stride];
     if (kind == VOID_KIND_I8) o = (uint8_t)quant_i8(x, s);
     else o = quant_e4m3(x, __fdiv_rn(1.0f, s));
   }
   q[(size_t)k * ldq + n] = o;
+}
+
+// absmax of a whole row-major [K, N] matrix into amax[0] (zero before the launch)
+__global__ void tensor_amax_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, float* __restrict__ amax) {
+  const int n = blockIdx.x * kColBlock + threadIdx.x;
+  const int k0 = blockIdx.y * kRowSlab;
+  const int k1 = (k0 + kRowSlab) < K ? (k0 + kRowSlab) : K;
+  float m = 0.0f;
+  if (n < N)
+    for (int k = k0; k < k1; ++k) m = fmaxf(m, fabsf(b[(size_t)k * ldb + n]));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));
 }
 
 // ------------------------------------------------------------------------------ Stream-K table
@@ -371,6 +384,17 @@ int void_quant_fp8_tiles(const float* values, int64_t nnz, uint8_t* q, float* sc
   return last_status();
 }
 
+static void quant_pass(const float* b, int64_t ldb, int K, int N, int kind, void* q, int64_t ldq, const float* scale,
+                       int scale_stride, cudaStream_t st) {
+  // blockIdx.y is limited to 65535: quantise in slabs of rows
+  for (int k0 = 0; k0 < K; k0 += 65535) {
+    const int kk = (K - k0) < 65535 ? (K - k0) : 65535;
+    dim3 g2((unsigned)((ldq + 255) / 256), kk);
+    quant_cols_kernel<<<g2, 256, 0, st>>>(b + (size_t)k0 * ldb, ldb, kk, N, kind,
+                                          reinterpret_cast<uint8_t*>(q) + (size_t)k0 * ldq, ldq, scale, scale_stride);
+  }
+}
+
 int void_quant_cols(const float* b, int64_t ldb, int32_t K, int32_t N, int32_t kind, void* q, int64_t ldq,
                     float* col_scale, float* col_scale_inv, void_stream_t stream) {
   if (K < 0 || N < 0 || (kind != VOID_KIND_I8 && kind != VOID_KIND_F8E4M3)) return VOID_ERR_BAD_ARG;
@@ -383,18 +407,23 @@ int void_quant_cols(const float* b, int64_t ldb, int32_t K, int32_t N, int32_t k
   dim3 g1((N + kColBlock - 1) / kColBlock, (K + kRowSlab - 1) / kRowSlab);
   col_amax_kernel<<<g1, kColBlock, 0, st>>>(b, ldb, K, N, col_scale);
   col_scale_kernel<<<(N + 255) / 256, 256, 0, st>>>(col_scale, col_scale_inv, N, kind);
-  if (K > 65535) {
-    // blockIdx.y is limited to 65535: quantise in slabs of rows
-    for (int k0 = 0; k0 < K; k0 += 65535) {
-      const int kk = (K - k0) < 65535 ? (K - k0) : 65535;
-      dim3 g2((unsigned)((ldq + 255) / 256), kk);
-      quant_cols_kernel<<<g2, 256, 0, st>>>(b + (size_t)k0 * ldb, ldb, kk, N, kind,
-                                            reinterpret_cast<uint8_t*>(q) + (size_t)k0 * ldq, ldq, col_scale);
-    }
-  } else {
-    dim3 g2((unsigned)((ldq + 255) / 256), K);
-    quant_cols_kernel<<<g2, 256, 0, st>>>(b, ldb, K, N, kind, reinterpret_cast<uint8_t*>(q), ldq, col_scale);
-  }
+  quant_pass(b, ldb, K, N, kind, q, ldq, col_scale, 1, st);
+  return last_status();
+}
+
+int void_quant_i8_tensor(const float* b, int64_t ldb, int32_t K, int32_t N, void* q, int64_t ldq, float* scale,
+                         void_stream_t stream) {
+  if (K < 0 || N < 0) return VOID_ERR_BAD_ARG;
+  if (b == nullptr || q == nullptr || scale == nullptr) return VOID_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  if (cudaMemsetAsync(scale, 0, 4, st) != cudaSuccess) return VOID_ERR_CUDA;
+  if (K == 0 || N == 0) return VOID_OK;
+  if (ldb < N || ldq < N) return VOID_ERR_SHAPE;
+  if (K > 65535 * kRowSlab) return VOID_ERR_TOO_LARGE;
+  dim3 g1((N + kColBlock - 1) / kColBlock, (K + kRowSlab - 1) / kRowSlab);
+  tensor_amax_kernel<<<g1, kColBlock, 0, st>>>(b, ldb, K, N, scale);
+  col_scale_kernel<<<1, 32, 0, st>>>(scale, nullptr, 1, VOID_KIND_I8);
+  quant_pass(b, ldb, K, N, VOID_KIND_I8, q, ldq, scale, 0, st);
   return last_status();
 }
 

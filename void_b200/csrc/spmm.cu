@@ -664,7 +664,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
   SpmmParams p;
-  p.tiles = reinterpret_cast<const uint8_t*>(a->tiles);
+  p.tiles = a->nnz > 0 ? reinterpret_cast<const uint8_t*>(a->tiles) : nullptr;  // null: no tensor map either
   p.tile_cols = a->tile_cols;
   p.tile_scales = a->tile_scales;
   p.row_ptr = a->row_ptr;

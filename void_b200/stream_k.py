@@ -1,0 +1,131 @@
+"""Stream-K load balancing for power-law tile-row lengths on B200.
+
+Mirrors StreamKWorkload (void/stream_k.py:13-33), compute_stream_k_workload (:36-110),
+void_spmm_stream_k (:233-301) and analyze_workload_balance (:467-492).
+
+The worker table is the reference's, bit for bit, but it is built by a device kernel instead of a
+Python loop with one .item() per row (:76-97).  The SpMM differs in how partial rows are joined:
+the reference lets every partial worker lock the output tile and read-modify-write it in the
+output dtype (:198-219, an unbounded spin); here consecutive workers of a row that land on the
+same CTA keep accumulating in tensor memory, rows that are shared between CTAs park int32
+partial sums, and the CTA that arrives last adds them and runs the epilogue - no lock, no wait,
+and an exact (integer) sum that does not depend on arrival order.
+"""
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib, _spmm
+from .int_quant import Int8VOIDTensor, _resolve_b
+
+
+@dataclass
+class StreamKWorkload:
+    """Per-worker assignments (void/stream_k.py:13-33)."""
+    worker_rows: torch.Tensor          # [n_workers] int32
+    worker_block_start: torch.Tensor   # [n_workers] int32
+    worker_block_end: torch.Tensor     # [n_workers] int32
+    worker_needs_atomic: torch.Tensor  # [n_workers] bool
+    n_workers: int
+    total_work: int
+    # extras used by the B200 launch (not part of the reference dataclass)
+    chunk_tiles: int = 0
+    worker_offsets: Optional[torch.Tensor] = None
+
+
+def compute_stream_k_workload(void_tensor, n_workers: Optional[int] = None,
+                              max_work_per_worker: int = 16) -> StreamKWorkload:
+    """Stream-K work distribution (void/stream_k.py:36-110): rows in order, every non-empty row cut
+    into chunks of target = min(ceil(n_blocks / n_workers), max_work_per_worker) tiles."""
+    row_ptr, _ = void_tensor.get_row_block_info()
+    nbr = void_tensor.block_grid[0]
+    rows, start, end, atomic, woff, target = _spmm.streamk_table(row_ptr, nbr, void_tensor.n_blocks, n_workers,
+                                                                  max_work_per_worker)
+    return StreamKWorkload(worker_rows=rows, worker_block_start=start, worker_block_end=end,
+                           worker_needs_atomic=atomic, n_workers=rows.numel(), total_work=void_tensor.n_blocks,
+                           chunk_tiles=target, worker_offsets=woff)
+
+
+def _plan_for(a: Int8VOIDTensor, packed, N: int, workload: StreamKWorkload, per_worker: bool, n_cta: Optional[int]):
+    panels = (N + 127) // 128
+    np_ = 4 if panels >= 4 else (2 if panels >= 2 else 1)
+    if n_cta is None:
+        n_cta = _spmm.sm_count(packed.tiles.device) * (1 if np_ == 4 else 2)
+    mode = 2 if per_worker else 1
+    key = ("streamk", N, np_, n_cta, mode, workload.chunk_tiles)
+    cache = getattr(a, "_plan_cache", None)
+    if cache is None:
+        cache = a._plan_cache = {}
+    plan = cache.get(key)
+    if plan is None:
+        plan = _spmm.make_plan(packed, N, np_, n_cta, mode, workload.chunk_tiles, workload.worker_offsets)
+        cache[key] = plan
+    return plan
+
+
+def void_spmm_stream_k(a: Int8VOIDTensor, b: torch.Tensor, workload: Optional[StreamKWorkload] = None,
+                       out: Optional[torch.Tensor] = None, *, b_scale=None, out_dtype: Optional[torch.dtype] = None,
+                       activation: int = 0, bias: Optional[torch.Tensor] = None,
+                       worker_partials: Optional[torch.Tensor] = None, acc_out: Optional[torch.Tensor] = None,
+                       n_cta: Optional[int] = None) -> torch.Tensor:
+    """Load-balanced INT8 SpMM (void/stream_k.py:233-301) with the fused epilogue of void_spmm_int8.
+
+    ``worker_partials`` (int32 [n_segments, 32, N], see the plan's segment list) makes every worker of
+    the table a segment of its own and records its partial sum - the check that the sum of the
+    partials is the row accumulator.
+    """
+    if not isinstance(a, Int8VOIDTensor):
+        raise NotImplementedError("void_spmm_stream_k on B200 takes an Int8VOIDTensor (quantize_void_tensor)")
+    assert b.dim() == 2
+    assert a.shape[1] == b.shape[0]
+    _lib.require_cuda(a.values, b)
+    M, K = a.shape
+    N = b.shape[1]
+    b_q, scalar, col_scale = _resolve_b(b, b_scale)
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or torch.float32, device=b.device)
+    packed = a.packed()
+    if a.n_blocks == 0:
+        return _spmm.spmm(packed, b_q, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=col_scale, b_scale=scalar,
+                          bias=bias, act=activation)
+    if workload is None:
+        # the table depends on A's structure only: built once per tensor, then reused
+        workload = getattr(a, "_streamk_workload_cache", None)
+        if workload is None or workload.total_work != a.n_blocks:
+            workload = compute_stream_k_workload(a)
+            a._streamk_workload_cache = workload
+    plan = _plan_for(a, packed, N, workload, worker_partials is not None, n_cta)
+    return _spmm.spmm(packed, b_q, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=col_scale, b_scale=scalar, bias=bias,
+                      act=activation, plan=plan, worker_partials=worker_partials, acc_out=acc_out)
+
+
+def stream_k_plan(a: Int8VOIDTensor, N: int, workload: StreamKWorkload, per_worker: bool = False,
+                  n_cta: Optional[int] = None) -> _spmm.Plan:
+    """The device-built work plan void_spmm_stream_k uses for an N-column product."""
+    return _plan_for(a, a.packed(), N, workload, per_worker, n_cta)
+
+
+def analyze_workload_balance(void_tensor) -> dict:
+    """Row-length statistics (void/stream_k.py:467-492)."""
+    row_ptr, _ = void_tensor.get_row_block_info()
+    row_work = (row_ptr[1:] - row_ptr[:-1]).float()
+    non_empty = row_work > 0
+    nz = row_work[non_empty]
+    if len(nz) == 0:
+        return {"empty": True}
+    return {
+        "empty": False,
+        "n_rows": len(row_work),
+        "n_nonempty_rows": non_empty.sum().item(),
+        "min_blocks_per_row": nz.min().item(),
+        "max_blocks_per_row": nz.max().item(),
+        "mean_blocks_per_row": nz.mean().item(),
+        "std_blocks_per_row": nz.std().item(),
+        "imbalance_ratio": (nz.max() / nz.mean()).item(),
+        "coefficient_of_variation": (nz.std() / nz.mean()).item(),
+    }
+
+
+__all__ = ["StreamKWorkload", "compute_stream_k_workload", "void_spmm_stream_k", "analyze_workload_balance",
+           "stream_k_plan"]
