@@ -41,7 +41,8 @@ enum {
   VOID_ERR_CUDA = -5,           /* a CUDA runtime / driver call failed                   */
   VOID_ERR_WORKSPACE = -6,      /* caller workspace too small                            */
   VOID_ERR_DEVICE_TIMEOUT = -7, /* a bounded device-side wait gave up (see status word)  */
-  VOID_ERR_TOO_LARGE = -8       /* size beyond a documented maximum                      */
+  VOID_ERR_TOO_LARGE = -8,      /* size beyond a documented maximum                      */
+  VOID_ERR_TENSOR_MAP = -9      /* the driver refused the copy-engine descriptor of B    */
 };
 
 /* element kinds of the 8-bit operands */
@@ -210,7 +211,9 @@ typedef struct void_spmm_args {
   int32_t panels_per_item; /* 128-column panels of B per work item: 1, 2 or 4            */
   int32_t stages;          /* shared-memory ring depth                                   */
   int32_t grid;            /* CTAs to launch without a plan                              */
-  int32_t reserved;
+  int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1, 2, 4 or 8      */
+  /* debugging aid: when not NULL, 64 uint64 nanosecond timestamps per launched CTA      */
+  void* trace;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

@@ -108,7 +108,7 @@ def test_int8_spmm_launch_shapes_agree():
     q = void.quantize_void_tensor(w.a)
     bq, bs = void.quantize_cols_int8(w.b)
     base = void.void_spmm_int8(q, bq, bs, out_dtype=torch.float16)
-    for np_, stages, grid in [(1, 3, 37), (2, 5, 0), (4, 2, 148), (4, 8, 1000)]:
+    for np_, stages, grid in [(1, 4, 37), (2, 5, 0), (4, 4, 148), (4, 5, 1000)]:
         out = torch.empty_like(base)
         _spmm.spmm(q.packed(), bq, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=bs, panels_per_item=np_,
                    stages=stages, grid=grid)

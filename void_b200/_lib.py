@@ -37,7 +37,8 @@ class SpmmArgs(ctypes.Structure):
         ("segs", c_vp), ("cta_seg_ptr", c_vp), ("n_cta", c_i32),
         ("partials", c_vp), ("partials_bytes", c_i64), ("counters", c_vp), ("worker_partials", c_vp),
         ("status", c_vp),
-        ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("reserved", c_i32),
+        ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
+        ("trace", c_vp),
     ]
 
 

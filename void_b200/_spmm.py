@@ -174,7 +174,7 @@ def prepare_b(b: torch.Tensor) -> torch.Tensor:
 def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode: int, col_scale=None,
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
-         grid: int = 0) -> torch.Tensor:
+         grid: int = 0, tiles_per_stage: int = 0, trace=None) -> torch.Tensor:
     """One launch of void_spmm_i8 / void_spmm_f8 on the current stream of b's device."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
@@ -219,7 +219,8 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
         panels_per_item = plan.np
     a.worker_partials = None if worker_partials is None else worker_partials.data_ptr()
     a.status = _lib.status_word(dev).data_ptr()
-    a.panels_per_item, a.stages, a.grid = panels_per_item, stages, grid
+    a.panels_per_item, a.stages, a.grid, a.tiles_per_stage = panels_per_item, stages, grid, tiles_per_stage
+    a.trace = None if trace is None else trace.data_ptr()
     fn = lib.void_spmm_i8 if packed.kind == _lib.KIND_I8 else lib.void_spmm_f8
     with torch.cuda.device(dev):
         _lib.check(fn(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm")

@@ -79,29 +79,17 @@ __global__ void rank_tiles_kernel(const int32_t* __restrict__ brow, const int32_
 }
 
 // ------------------------------------------------------------------------------ pack
-static int pack_layout() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("VOID_B200_DESC_VARIANT");
-    v = (e && (atoi(e) & 2)) ? 1 : 0;
-  }
-  return v;
-}
 // One thread per 16-byte chunk of the packed tile.  Packed chunk q of a tile holds bytes
 // [c16*16, c16*16+16) of tile row r with  q = (r/8)*16 + c16*8 + (r%8): four groups of eight
 // rows, each group stored as two 8x16-byte core matrices (k bytes 0..15, then 16..31).
 __global__ void pack_tiles_kernel(const uint4* __restrict__ values, const int32_t* __restrict__ block_indices,
-                                  int64_t nnz, uint4* __restrict__ packed, int layout) {
+                                  int64_t nnz, uint4* __restrict__ packed) {
   const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= nnz * 64) return;
   const int64_t j = g >> 6;
   const int q = (int)(g & 63);
-  int r = (q >> 4) * 8 + (q & 7);
-  int c16 = (q >> 3) & 1;
-  if (layout == 1) {  // debugging aid: row-major rows of 32 bytes with the 32-byte swizzle
-    r = q >> 1;
-    c16 = (q & 1) ^ ((r >> 2) & 1);
-  }
+  const int r = (q >> 4) * 8 + (q & 7);
+  const int c16 = (q >> 3) & 1;
   const int64_t src_tile = block_indices[j];
   packed[g] = values[src_tile * 64 + r * 2 + c16];
 }
@@ -301,6 +289,7 @@ const char* void_strerror(int status) {
     case VOID_ERR_WORKSPACE: return "workspace too small";
     case VOID_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     case VOID_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    case VOID_ERR_TENSOR_MAP: return "the driver refused the copy-engine (TMA) descriptor of B";
     default: return "unknown status";
   }
 }
@@ -350,7 +339,7 @@ int void_pack_tiles(const void* values, const float* scales, int64_t n_scales, c
       return VOID_ERR_ALIGN;
     if (scales != nullptr && n_scales != 1 && n_scales != nnz) return VOID_ERR_BAD_ARG;
     pack_tiles_kernel<<<(unsigned)((nnz * 64 + tb - 1) / tb), tb, 0, st>>>(
-        reinterpret_cast<const uint4*>(values), block_indices, nnz, reinterpret_cast<uint4*>(packed), pack_layout());
+        reinterpret_cast<const uint4*>(values), block_indices, nnz, reinterpret_cast<uint4*>(packed));
     gather_tile_meta_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_cols, scales, n_scales, block_indices,
                                                                            nnz, tile_cols, tile_scales);
   }

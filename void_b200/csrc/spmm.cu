@@ -8,13 +8,22 @@
 //
 // i.e. one tcgen05.mma (M=128, N=32, K=32) per (tile, 128-column panel of B).  The "A"
 // operand of the instruction is the B panel exactly as it lies in memory (n contiguous:
-// MN-major, 128-byte swizzle, written by a 2-D TMA load); the "B" operand is the packed tile
+// MN-major, 128-byte swizzle, written by a tiled TMA load); the "B" operand is the packed tile
 // (K-major, no swizzle, written by a linear bulk copy).  Accumulators live in tensor memory:
 // lane = output column n, column = tile row m.
 //
-// Warp roles in a 192-thread CTA: warp 0 streams tiles and panels into a shared-memory ring,
-// warp 1 issues the MMAs, warps 2..5 read accumulators back (each warp owns the 32 TMEM lanes
-// of its quadrant), apply scales / bias / activation and store C.
+// Warp roles: warps 0..3 stream tiles and panels into a shared-memory ring, warp 4 issues the
+// MMAs, warps 5..12 read accumulators back (two warps per 32-lane TMEM quadrant, each taking
+// half of the 32 accumulator columns), apply scales / bias / activation and store C.
+//
+// The ring moves GROUPS of up to `group` consecutive tiles of a tile row per stage.  Measured on
+// B200, one turn of a stage by one thread (wait for the slot, expect_tx, issue the copies) costs
+// about 300 ns whatever the bytes, so the stream is latency-bound on the issuing thread, not on
+// the copy engine: a group needs one wait + one expect_tx + one bulk copy (its tiles are
+// contiguous in the packed store) and one tiled TMA per tile, the TMAs issued by different lanes
+// in the same instruction, and the four producer warps take the groups round-robin so that four
+// stage turns are in flight at once.  When N is a multiple of 128 the TMA is 3-D (B viewed as
+// [panel][k][128 columns]) and fetches all panels of the work item at once.
 //
 // Two kernels share this pipeline:
 //   spmm_rowacc_kernel  one accumulator per (tile row, column chunk), scaled once by the
@@ -41,8 +50,13 @@ constexpr int kPanelN = 128;
 constexpr int kPanelBytes = kTile * kPanelN;  // 4096
 constexpr int kMaxStages = 16;
 constexpr int kMaxSlots = 16;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kProducerWarps = 4;   // warps 0..3 stream tiles and panels
+constexpr int kMmaWarp = kProducerWarps;  // warp 4 issues the MMAs (and owns the TMEM allocation)
+constexpr int kFirstEpiWarp = kMmaWarp + 1;
+constexpr int kEpiWarps = 8;        // warps 5..12: two per TMEM lane quadrant
+constexpr int kEpiThreads = 32 * kEpiWarps;
+constexpr int kThreads = 32 * kFirstEpiWarp + kEpiThreads;
+constexpr int kColsPerWarp = 32 / (kEpiWarps / 4);  // accumulator columns one epilogue warp reads
 
 // device status codes (written to the status word)
 constexpr int kStatusTimeout = 1;
@@ -67,13 +81,20 @@ struct SpmmParams {
   int32_t* counters;
   int32_t* worker_partials;
   int32_t* status;
-  int np;      // panels per work item
-  int stages;  // ring depth
-  int n_items; // without a plan: nbr * n_chunks
+  unsigned long long* trace;  // debugging aid: 64 timestamps per CTA, or null
+  int np;       // panels per work item
+  int group;    // tiles per ring stage
+  int stages;   // ring depth
+  int use3d;    // B panels of a tile fetched by one 3-D TMA
+  int n_items;  // without a plan: nbr * n_chunks
   unsigned long long desc_hi_a;  // B panel  (instruction operand A: MN-major, 128B swizzle)
   unsigned long long desc_hi_b;  // A tile   (instruction operand B: K-major, no swizzle)
   unsigned int idesc;
 };
+
+__device__ __forceinline__ void stamp(const SpmmParams& p, int slot) {
+  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + slot] = globaltimer_ns();
+}
 
 struct Seg {
   int row, chunk, t0, t1, nseg, slot0, my_idx, ctr;
@@ -122,57 +143,116 @@ __device__ __forceinline__ float gelu_tanh_sigmoid(float x) {
   const float t = 2.0f * sig - 1.0f;
   return x * 0.5f * (1.0f + t);
 }
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case VOID_ACT_RELU: return fmaxf(x, 0.0f);
-    case VOID_ACT_GELU: return gelu_tanh_sigmoid(x);
-    case VOID_ACT_SILU: return x * (1.0f / (1.0f + expf(-x)));
-    default: return x;
-  }
+// What an epilogue thread needs to know about C, read from the kernel parameters once.
+struct OutDesc {
+  void* out;
+  long long ldc;
+  void* acc_out;
+  int M, N, dtype, act;
+};
+__device__ __forceinline__ OutDesc out_desc(const SpmmParams& p) {
+  OutDesc o;
+  o.out = p.out; o.ldc = p.ldc; o.acc_out = p.acc_out; o.M = p.M; o.N = p.N; o.dtype = p.out_dtype; o.act = p.act;
+  return o;
 }
 
-// Store 32 finished values of one output column n (tile rows m = 0..31 of tile row `row`).
-__device__ __forceinline__ void store_column(const SpmmParams& p, int row, int n, const float (&v)[32]) {
-  if (n >= p.N) return;
-  const int r0 = row * kTile;
-  const int rows = (p.M - r0) < kTile ? (p.M - r0) : kTile;
-  if (p.out_dtype == VOID_OUT_F16) {
-    __half* o = reinterpret_cast<__half*>(p.out) + (size_t)r0 * p.ldc + n;
+// Store eight finished values of output column n: matrix rows row*32 + m0 .. + 7.
+__device__ __forceinline__ void store8(const OutDesc& o, int row, int n, int m0, float (&v)[8]) {
+  const int r0 = row * kTile + m0;
+  const int rows = o.M - r0;  // rows left below r0
+  switch (o.act) {
+    case VOID_ACT_RELU:
 #pragma unroll
-    for (int m = 0; m < 32; ++m)
-      if (m < rows) o[(size_t)m * p.ldc] = __float2half_rn(v[m]);
-  } else if (p.out_dtype == VOID_OUT_BF16) {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)r0 * p.ldc + n;
+      for (int k = 0; k < 8; ++k) v[k] = fmaxf(v[k], 0.0f);
+      break;
+    case VOID_ACT_GELU:
 #pragma unroll
-    for (int m = 0; m < 32; ++m)
-      if (m < rows) o[(size_t)m * p.ldc] = __float2bfloat16_rn(v[m]);
+      for (int k = 0; k < 8; ++k) v[k] = gelu_tanh_sigmoid(v[k]);
+      break;
+    case VOID_ACT_SILU:
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = v[k] * (1.0f / (1.0f + expf(-v[k])));
+      break;
+    default:
+      break;
+  }
+  if (o.dtype == VOID_OUT_F16) {
+    __half* dst = reinterpret_cast<__half*>(o.out) + (size_t)r0 * o.ldc + n;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < rows) dst[(size_t)k * o.ldc] = __float2half_rn(v[k]);
+  } else if (o.dtype == VOID_OUT_BF16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(o.out) + (size_t)r0 * o.ldc + n;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < rows) dst[(size_t)k * o.ldc] = __float2bfloat16_rn(v[k]);
   } else {
-    float* o = reinterpret_cast<float*>(p.out) + (size_t)r0 * p.ldc + n;
+    float* dst = reinterpret_cast<float*>(o.out) + (size_t)r0 * o.ldc + n;
 #pragma unroll
-    for (int m = 0; m < 32; ++m)
-      if (m < rows) o[(size_t)m * p.ldc] = v[m];
+    for (int k = 0; k < 8; ++k)
+      if (k < rows) dst[(size_t)k * o.ldc] = v[k];
   }
 }
 
-// Epilogue of one output column: raw accumulators -> dequantised, biased, activated values.
+// Epilogue of eight raw accumulators of one output column: dequantise, bias, activation, store.
 template <int KIND>
-__device__ __forceinline__ void finish_column(const SpmmParams& p, int row, int n, const uint32_t (&r)[32],
-                                              float row_scale) {
-  if (n >= p.N) return;
-  if (p.acc_out != nullptr) {
-    uint32_t* a = reinterpret_cast<uint32_t*>(p.acc_out) + (size_t)row * kTile * p.N + n;
+__device__ __forceinline__ void finish8(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[8],
+                                        float row_scale, float cs, float bias) {
+  if (n >= o.N) return;
+  if (o.acc_out != nullptr) {
+    uint32_t* a = reinterpret_cast<uint32_t*>(o.acc_out) + ((size_t)row * kTile + m0) * o.N + n;
 #pragma unroll
-    for (int m = 0; m < 32; ++m) a[(size_t)m * p.N] = r[m];
+    for (int k = 0; k < 8; ++k) a[(size_t)k * o.N] = r[k];
   }
-  const float cs = (p.col_scale != nullptr) ? __ldg(p.col_scale + n) * p.b_scale : p.b_scale;
-  const float bias = (p.bias != nullptr) ? __ldg(p.bias + n) : 0.0f;
-  float v[32];
+  float v[8];
 #pragma unroll
-  for (int m = 0; m < 32; ++m) {
-    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
-    v[m] = apply_act((x * row_scale) * cs + bias, p.act);
+  for (int k = 0; k < 8; ++k) {
+    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
+    v[k] = (x * row_scale) * cs + bias;
   }
-  store_column(p, row, n, v);
+  store8(o, row, n, m0, v);
+}
+
+// Fast epilogue of one warp's share of a panel: kColsPerWarp raw accumulators of output column n
+// straight to C (no raw-accumulator dump, no split row), stores specialised per output type.
+template <int KIND>
+__device__ __forceinline__ void finish_cols(const OutDesc& o, int row, int n, int m0,
+                                            const uint32_t (&r)[kColsPerWarp], float row_scale, float cs,
+                                            float bias) {
+  if (n >= o.N) return;
+  float v[kColsPerWarp];
+#pragma unroll
+  for (int k = 0; k < kColsPerWarp; ++k) {
+    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
+    v[k] = (x * row_scale) * cs + bias;
+  }
+  if (o.act != VOID_ACT_NONE) {
+#pragma unroll
+    for (int k = 0; k < kColsPerWarp; ++k) {
+      if (o.act == VOID_ACT_GELU) v[k] = gelu_tanh_sigmoid(v[k]);
+      else if (o.act == VOID_ACT_RELU) v[k] = fmaxf(v[k], 0.0f);
+      else v[k] = v[k] * (1.0f / (1.0f + expf(-v[k])));
+    }
+  }
+  const int r0 = row * kTile + m0;
+  const int rows = o.M - r0;
+  const size_t first = (size_t)r0 * o.ldc + n;
+  if (o.dtype == VOID_OUT_F16) {
+    __half* dst = reinterpret_cast<__half*>(o.out) + first;
+#pragma unroll
+    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+      if (k < rows) *dst = __float2half_rn(v[k]);
+  } else if (o.dtype == VOID_OUT_BF16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(o.out) + first;
+#pragma unroll
+    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+      if (k < rows) *dst = __float2bfloat16_rn(v[k]);
+  } else {
+    float* dst = reinterpret_cast<float*>(o.out) + first;
+#pragma unroll
+    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+      if (k < rows) *dst = v[k];
+  }
 }
 
 struct __align__(8) PipeBars {
@@ -182,38 +262,67 @@ struct __align__(8) PipeBars {
   uint64_t acc_empty[kMaxSlots];
 };
 
-// warp 0: stream (tile, panels) units of this CTA's segments into the ring.
+// shared-memory offsets inside one ring stage
+__device__ __forceinline__ uint32_t panel_off(const SpmmParams& p, int j, int q) {
+  return (uint32_t)(j * p.np + q) * kPanelBytes;
+}
+__device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
+  return (uint32_t)(p.group * p.np) * kPanelBytes + (uint32_t)j * kTileBytes;
+}
+
+// Producer warp `pw` of kProducerWarps: the CTA's groups of tiles are numbered in the order the
+// MMA warp consumes them; group g uses ring stage g % stages and belongs to warp g % kProducerWarps.
 __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtensorMap* tmap, PipeBars* bars,
                                               uint32_t ring_base, uint32_t stage_bytes, volatile int* abort_flag,
-                                              int lane) {
+                                              int lane, int pw) {
   int begin, end, step;
   seg_range(p, begin, end, step);
-  int stage = 0;
-  uint32_t phase = 0;
+  const int G = p.group;
+  int g = 0;  // groups of all earlier segments
   for (int i = begin; i < end; i += step) {
     const Seg s = load_seg(p, i);
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
-    for (int tb = s.t0; tb < s.t1; tb += 32) {
-      const int cnt = (s.t1 - tb) < 32 ? (s.t1 - tb) : 32;
-      const int my_col = (lane < cnt) ? __ldg(p.tile_cols + tb + lane) : 0;
-      for (int j = 0; j < cnt; ++j) {
-        const int col = __shfl_sync(0xffffffffu, my_col, j);
-        int ok = 1;
-        if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return;
-        if (lane == 0) {
-          const uint32_t full = smem_u32(&bars->full[stage]);
-          const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
-          mbar_expect_tx(full, (uint32_t)(kTileBytes + npan * kPanelBytes));
-          bulk_load(sbase + (uint32_t)p.np * kPanelBytes, p.tiles + (size_t)(tb + j) * kTileBytes, kTileBytes, full);
-          for (int q = 0; q < npan; ++q)
-            tma_load_2d(sbase + (uint32_t)q * kPanelBytes, tmap, n0 + q * kPanelN, col * kTile, full);
+    const uint32_t unit_bytes = (uint32_t)(kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes);
+    const int ngroups = (s.t1 - s.t0 + G - 1) / G;
+    int k = pw - g % kProducerWarps;
+    if (k < 0) k += kProducerWarps;
+    // block column of this lane's tile in the warp's next group, fetched one group ahead
+    int col = 0;
+    if (k < ngroups && lane < G && s.t0 + k * G + lane < s.t1) col = __ldg(p.tile_cols + s.t0 + k * G + lane);
+    for (; k < ngroups; k += kProducerWarps) {
+      const int gi = g + k;
+      const int stage = gi % p.stages;
+      const uint32_t phase = (uint32_t)(gi / p.stages) & 1u;
+      const int t = s.t0 + k * G;
+      const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
+      const int kn = k + kProducerWarps;
+      int col_next = 0;
+      if (kn < ngroups && lane < G && s.t0 + kn * G + lane < s.t1) col_next = __ldg(p.tile_cols + s.t0 + kn * G + lane);
+      const uint32_t full = smem_u32(&bars->full[stage]);
+      const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag) ? 1 : 0;
+        if (ok) {
+          mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
+          bulk_load(sbase + tile_off(p, 0), p.tiles + (size_t)t * kTileBytes, (uint32_t)gcnt * kTileBytes, full);
         }
-        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      if (lane < gcnt) {
+        if (p.use3d) {
+          tma_load_3d(sbase + panel_off(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np, full);
+        } else {
+          for (int q = 0; q < npan; ++q)
+            tma_load_2d(sbase + panel_off(p, lane, q), tmap, n0 + q * kPanelN, col * kTile, full);
+        }
+      }
+      if (lane == 0 && p.trace != nullptr && i == begin && k < 16) stamp(p, 32 + k);
+      col = col_next;
     }
+    g += ngroups;
   }
 }
 
@@ -223,12 +332,56 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, ui
   else mma_f8(d, a, b, idesc, acc);
 }
 
+__device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtensorMap* tmap, PipeBars& bars,
+                                               uint32_t* tmem_base_s, int* abort_s, int n_acc, uint32_t tmem_cols) {
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    *abort_s = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&bars.full[s]), 1);
+      mbar_init(smem_u32(&bars.empty[s]), 1);
+    }
+    for (int b = 0; b < n_acc; ++b) {
+      mbar_init(smem_u32(&bars.acc_full[b]), 1);
+      mbar_init(smem_u32(&bars.acc_empty[b]), kEpiWarps);
+    }
+    fence_mbar_init();
+    if (p.tiles != nullptr) prefetch_tmap(tmap);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_base_s), tmem_cols);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) stamp(p, 0);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 0) stamp(p, 1);
+}
+
+__device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abort_s, uint32_t tmem_base,
+                                                  uint32_t tmem_cols) {
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 0) stamp(p, 7);
+  if (*abort_s) {
+    // let copies that may still be in flight land before shared memory is given back
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusTimeout);
+    __syncthreads();
+  }
+  if ((threadIdx.x >> 5) == kMmaWarp) tmem_dealloc(tmem_base, tmem_cols);
+}
+
 // ------------------------------------------------------------------------------------------
 // Row-accumulate kernel.
 // ------------------------------------------------------------------------------------------
 template <int KIND>
 __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
-                                                               const SpmmParams p) {
+                                                               const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   __shared__ uint32_t tmem_base_s;
@@ -239,43 +392,34 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t stage_bytes = (uint32_t)(p.np * kPanelBytes + kTileBytes);
+  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes));
   const uint32_t acc_cols = (uint32_t)p.np * 32u;  // TMEM columns of one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
   volatile int* abort_flag = &abort_s;
 
-  if (threadIdx.x == 0) {
-    abort_s = 0;
-    last_s = 0;
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&bars.full[s]), 1);
-      mbar_init(smem_u32(&bars.empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bars.acc_full[b]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[b]), 4);
-    }
-    fence_mbar_init();
-    if (p.tiles != nullptr) prefetch_tmap(&tmap_b);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+  if (threadIdx.x == 0) last_s = 0;
+  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == 0) {
-    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane);
-  } else if (warp == 1) {
+  if (warp < kProducerWarps) {
+    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+    if (warp == 0 && lane == 0) stamp(p, 2);
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
+      // Everything an MMA needs is kept in registers and advanced by constants: this thread runs
+      // alone on its scheduler, so every dependent instruction between two MMAs costs its full
+      // latency.
+      const uint32_t idesc = p.idesc;
+      const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
+      const int G = p.group, S = p.stages, np = p.np;
+      const uint32_t tiles_at = (uint32_t)(G * np) * kPanelBytes;
+      constexpr uint64_t kPanelStep = kPanelBytes >> 4, kTileStep = kTileBytes >> 4;
       int begin, end, step;
       seg_range(p, begin, end, step);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t sbase = ring_base;
       uint32_t it = 0;
       bool ok = true;
       for (int i = begin; i < end && ok; i += step, ++it) {
@@ -286,30 +430,59 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
         if (!ok) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * acc_cols;
-        for (int t = s.t0; t < s.t1; ++t) {
+        uint32_t acc = 0u;
+        int gidx = 0;
+        for (int t = s.t0; t < s.t1; t += G, ++gidx) {
+          const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
+          if (p.trace != nullptr && i == begin && gidx < 8) stamp(p, 48 + gidx);
           ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
           if (!ok) break;
+          if (p.trace != nullptr && i == begin && gidx < 16) stamp(p, 16 + gidx);
           tc_fence_after();
-          const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
-          const uint64_t bdesc = smem_desc(p.desc_hi_b, sbase + (uint32_t)p.np * kPanelBytes);
-          for (int q = 0; q < npan; ++q) {
-            const uint64_t adesc = smem_desc(p.desc_hi_a, sbase + (uint32_t)q * kPanelBytes);
-            issue_mma<KIND>(d0 + (uint32_t)q * 32u, adesc, bdesc, p.idesc, t > s.t0 ? 1u : 0u);
+          const bool trc = p.trace != nullptr && i == begin && gidx == 1;
+          long long ck[6] = {0, 0, 0, 0, 0, 0};
+          if (trc) ck[0] = clock64();
+          uint64_t ad = smem_desc(hi_a, sbase);
+          uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
+          for (int j = 0; j < gcnt; ++j) {
+            uint64_t adq = ad;
+            uint32_t d = d0;
+            for (int q = 0; q < npan; ++q) {
+              issue_mma<KIND>(d, adq, bd, idesc, acc);
+              adq += kPanelStep;
+              d += 32u;
+            }
+            ad += kPanelStep * (uint64_t)np;
+            bd += kTileStep;
+            acc = 1u;
+            if (trc && j < 4) ck[1 + j] = clock64();
           }
           tc_commit(smem_u32(&bars.empty[stage]));
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          if (trc) {
+            ck[5] = clock64();
+            unsigned long long* tp = p.trace + (size_t)blockIdx.x * 64 + 56;
+            for (int z = 0; z < 6; ++z) tp[z] = ck[z] - ck[0];
+          }
+          sbase += stage_bytes;
+          if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
         if (!ok) break;
         if (s.t1 > s.t0) tc_commit(smem_u32(&bars.acc_full[buf]));
         else mbar_arrive(smem_u32(&bars.acc_full[buf]));
+        if (i == begin) stamp(p, 3);
       }
+      stamp(p, 4);
     }
     __syncwarp();
   } else {
-    // epilogue warps 2..5; TMEM lane quadrant = warp id mod 4
+    // epilogue warps: TMEM lane quadrant = warp id mod 4; the two warps of a quadrant split the
+    // 32 accumulator columns (tile rows m) in halves
     const int quad = warp & 3;
-    const int epi_tid = (int)threadIdx.x - 64;
+    const int half = (warp - kFirstEpiWarp) >> 2;
+    const int epi_tid = (int)threadIdx.x - 32 * kFirstEpiWarp;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    const int m_first = half * kColsPerWarp;
+    const OutDesc od = out_desc(p);
     int begin, end, step;
     seg_range(p, begin, end, step);
     uint32_t it = 0;
@@ -319,97 +492,136 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
       const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
       const bool has = s.t1 > s.t0;
       const float rs = (p.row_scale != nullptr) ? __ldg(p.row_scale + s.row) : 1.0f;
-      // one thread waits, the named barrier hands its verdict to all four epilogue warps, so
-      // that they leave the loop together if the wait gave up
-      if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, abort_flag) ? 1 : 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!ok_s[it & 1u]) break;
-      tc_fence_after();
       const int n_base = s.chunk * p.np * kPanelN + quad * 32 + lane;
+      // per-column scale and bias of the first panel are fetched before the accumulator is ready
+      float cs = p.b_scale, bias = 0.0f;
+      if (n_base < p.N) {
+        if (p.col_scale != nullptr) cs = __ldg(p.col_scale + n_base) * p.b_scale;
+        if (p.bias != nullptr) bias = __ldg(p.bias + n_base);
+      }
+      // one thread waits, the named barrier hands its verdict to all epilogue warps, so that they
+      // leave the loop together if the wait gave up
+      if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, abort_flag) ? 1 : 0;
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      if (!ok_s[it & 1u]) break;
+      if (epi_tid == 0 && i == begin) stamp(p, 5);
+      if (epi_tid == 0) stamp(p, 8);
+      tc_fence_after();
+      const bool fast = s.nseg == 1 && od.acc_out == nullptr && p.worker_partials == nullptr;
+#pragma unroll 1
       for (int q = 0; q < npan; ++q) {
-        uint32_t r[32];
-        if (has) {
-          tmem_ld_32x32(tmem_base + lane_sel + buf * acc_cols + (uint32_t)q * 32u, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int m = 0; m < 32; ++m) r[m] = 0u;
-        }
-        if (q == npan - 1) {  // accumulator buffer is free again
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-        }
         const int n = n_base + q * kPanelN;
-        if (p.worker_partials != nullptr && n < p.N) {
-          uint32_t* w = reinterpret_cast<uint32_t*>(p.worker_partials) + ((size_t)i * kTile) * p.N + n;
-#pragma unroll
-          for (int m = 0; m < 32; ++m) w[(size_t)m * p.N] = r[m];
+        float cs_next = p.b_scale, bias_next = 0.0f;
+        if (q + 1 < npan && n + kPanelN < p.N) {
+          if (p.col_scale != nullptr) cs_next = __ldg(p.col_scale + n + kPanelN) * p.b_scale;
+          if (p.bias != nullptr) bias_next = __ldg(p.bias + n + kPanelN);
         }
-        if (s.nseg == 1) {
-          finish_column<KIND>(p, s.row, n, r, rs);
-        } else {
-          // partial sum of a split row: park it, 128 contiguous bytes per thread
-          uint4* dst = reinterpret_cast<uint4*>(p.partials) +
-                       (((size_t)(s.slot0 + s.my_idx) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8;
+        if (fast) {
+          uint32_t r[kColsPerWarp];
+          if (has) {
+            const uint32_t taddr = tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first);
+            if (kColsPerWarp == 16) tmem_ld_32x16(taddr, reinterpret_cast<uint32_t(&)[16]>(r));
+            else tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r));
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) dst[c] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+            for (int k = 0; k < kColsPerWarp; ++k) r[k] = 0u;
+          }
+          if (q == npan - 1) {  // this warp is done with the accumulator buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+          }
+          finish_cols<KIND>(od, s.row, n, m_first, r, rs, cs, bias);
+          cs = cs_next;
+          bias = bias_next;
+          continue;
         }
+#pragma unroll 1
+        for (int c = 0; c < kColsPerWarp; c += 8) {
+          const int m0 = m_first + c;
+          uint32_t r[8];
+          if (has) {
+            tmem_ld_32x8(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m0), r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r[k] = 0u;
+          }
+          if (epi_tid == 0 && q == 0) stamp(p, 9 + (c >> 3) * 2);
+          if (q == npan - 1 && c + 8 >= kColsPerWarp) {  // this warp is done with the accumulator buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+          }
+          if (p.worker_partials != nullptr && n < p.N) {
+            uint32_t* w = reinterpret_cast<uint32_t*>(p.worker_partials) + ((size_t)i * kTile + m0) * p.N + n;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) w[(size_t)k * p.N] = r[k];
+          }
+          if (s.nseg == 1) {
+            finish8<KIND>(od, s.row, n, m0, r, rs, cs, bias);
+            if (epi_tid == 0 && q == 0) stamp(p, 10 + (c >> 3) * 2);
+          } else {
+            // partial sum of a split row: park it (per thread 32 contiguous ints per panel)
+            uint4* dst = reinterpret_cast<uint4*>(p.partials) +
+                         (((size_t)(s.slot0 + s.my_idx) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8 + (m0 >> 2);
+            dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+            dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+          }
+        }
+        cs = cs_next;
+        bias = bias_next;
       }
       if (s.nseg > 1) {
         // the CTA that arrives last adds the parked partial sums and finishes the row
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (epi_tid == 0) {
           const int old = atomicAdd(p.counters + s.ctr, 1);
           const int last = (old == s.nseg - 1) ? 1 : 0;
           if (last) p.counters[s.ctr] = 0;  // left clean for the next launch
           last_s = last;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         const int last = last_s;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (last) {
           __threadfence();
+#pragma unroll 1
           for (int q = 0; q < npan; ++q) {
-            uint32_t r[32];
+            const int n = n_base + q * kPanelN;
+            float csq = p.b_scale, biasq = 0.0f;
+            if (n < p.N) {
+              if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+              if (p.bias != nullptr) biasq = __ldg(p.bias + n);
+            }
+#pragma unroll 1
+            for (int c = 0; c < kColsPerWarp; c += 8) {
+              const int m0 = m_first + c;
+              uint32_t r[8];
 #pragma unroll
-            for (int m = 0; m < 32; ++m) r[m] = 0u;
-            for (int j = 0; j < s.nseg; ++j) {
-              const uint4* src = reinterpret_cast<const uint4*>(p.partials) +
-                                 (((size_t)(s.slot0 + j) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8;
+              for (int k = 0; k < 8; ++k) r[k] = 0u;
+              for (int j = 0; j < s.nseg; ++j) {
+                const uint4* src = reinterpret_cast<const uint4*>(p.partials) +
+                                   (((size_t)(s.slot0 + j) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8 + (m0 >> 2);
+                const uint4 a = __ldcg(src), b = __ldcg(src + 1);
+                const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const uint4 v = __ldcg(src + c);
-                if (KIND == VOID_KIND_I8) {
-                  r[4 * c] += v.x; r[4 * c + 1] += v.y; r[4 * c + 2] += v.z; r[4 * c + 3] += v.w;
-                } else {
-                  r[4 * c] = __float_as_uint(__uint_as_float(r[4 * c]) + __uint_as_float(v.x));
-                  r[4 * c + 1] = __float_as_uint(__uint_as_float(r[4 * c + 1]) + __uint_as_float(v.y));
-                  r[4 * c + 2] = __float_as_uint(__uint_as_float(r[4 * c + 2]) + __uint_as_float(v.z));
-                  r[4 * c + 3] = __float_as_uint(__uint_as_float(r[4 * c + 3]) + __uint_as_float(v.w));
+                for (int k = 0; k < 8; ++k) {
+                  if (KIND == VOID_KIND_I8) r[k] += v[k];
+                  else r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(v[k]));
                 }
               }
+              finish8<KIND>(od, s.row, n, m0, r, rs, csq, biasq);
             }
-            finish_column<KIND>(p, s.row, n_base + q * kPanelN, r, rs);
           }
         }
       }
     }
+    if (epi_tid == 0) stamp(p, 6);
   }
-
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (abort_s) {
-    // let copies that may still be in flight land before shared memory is given back
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) {
-    }
-    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusTimeout);
-    __syncthreads();
-  }
-  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  pipeline_teardown(p, &abort_s, tmem_base, tmem_cols);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -417,7 +629,7 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
 // ------------------------------------------------------------------------------------------
 template <int KIND, int NP>
 __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_constant__ CUtensorMap tmap_b,
-                                                              const SpmmParams p) {
+                                                              const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   __shared__ uint32_t tmem_base_s;
@@ -426,71 +638,73 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
   constexpr uint32_t kSlotCols = NP * 32;
   constexpr uint32_t kTmemCols = 512;
   constexpr int kSlots = (kTmemCols / kSlotCols) < kMaxSlots ? (kTmemCols / kSlotCols) : kMaxSlots;
+  constexpr int CW = kColsPerWarp;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t stage_bytes = (uint32_t)(NP * kPanelBytes + kTileBytes);
+  const uint32_t stage_bytes = (uint32_t)(p.group * (NP * kPanelBytes + kTileBytes));
   volatile int* abort_flag = &abort_s;
 
-  if (threadIdx.x == 0) {
-    abort_s = 0;
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&bars.full[s]), 1);
-      mbar_init(smem_u32(&bars.empty[s]), 1);
-    }
-    for (int b = 0; b < kSlots; ++b) {
-      mbar_init(smem_u32(&bars.acc_full[b]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[b]), 4);
-    }
-    fence_mbar_init();
-    if (p.tiles != nullptr) prefetch_tmap(&tmap_b);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, kSlots, kTmemCols);
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == 0) {
-    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane);
-  } else if (warp == 1) {
+  if (warp < kProducerWarps) {
+    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+    if (warp == 0 && lane == 0) stamp(p, 2);
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
+      const uint32_t idesc = p.idesc;
+      const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
+      const int G = p.group, S = p.stages;
+      const uint32_t tiles_at = (uint32_t)(G * NP) * kPanelBytes;
+      constexpr uint64_t kPanelStep = kPanelBytes >> 4, kTileStep = kTileBytes >> 4;
       int begin, end, step;
       seg_range(p, begin, end, step);
       int stage = 0, slot = 0;
       uint32_t phase = 0, sphase = 0;
+      uint32_t sbase = ring_base;
       bool ok = true;
       for (int i = begin; i < end && ok; i += step) {
         const Seg s = load_seg(p, i);
         const int npan = panels_in_chunk(p, s.chunk);
-        for (int t = s.t0; t < s.t1; ++t) {
+        for (int t = s.t0; t < s.t1 && ok; t += G) {
+          const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
           ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
           if (!ok) break;
-          ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
-          const uint64_t bdesc = smem_desc(p.desc_hi_b, sbase + (uint32_t)NP * kPanelBytes);
-          const uint32_t d0 = tmem_base + (uint32_t)slot * kSlotCols;
-          for (int q = 0; q < npan; ++q) {
-            const uint64_t adesc = smem_desc(p.desc_hi_a, sbase + (uint32_t)q * kPanelBytes);
-            issue_mma<KIND>(d0 + (uint32_t)q * 32u, adesc, bdesc, p.idesc, 0u);
+          uint64_t ad = smem_desc(hi_a, sbase);
+          uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
+          for (int j = 0; j < gcnt; ++j) {
+            ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            uint64_t adq = ad;
+            uint32_t d = tmem_base + (uint32_t)slot * kSlotCols;
+            for (int q = 0; q < npan; ++q) {
+              issue_mma<KIND>(d, adq, bd, idesc, 0u);
+              adq += kPanelStep;
+              d += 32u;
+            }
+            tc_commit(smem_u32(&bars.acc_full[slot]));
+            ad += kPanelStep * (uint64_t)NP;
+            bd += kTileStep;
+            if (++slot == kSlots) { slot = 0; sphase ^= 1u; }
           }
+          if (!ok) break;
           tc_commit(smem_u32(&bars.empty[stage]));
-          tc_commit(smem_u32(&bars.acc_full[slot]));
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-          if (++slot == kSlots) { slot = 0; sphase ^= 1u; }
+          sbase += stage_bytes;
+          if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
       }
+      stamp(p, 4);
     }
     __syncwarp();
   } else {
     const int quad = warp & 3;
+    const int half = (warp - kFirstEpiWarp) >> 2;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    const int m_first = half * CW;
+    const OutDesc od = out_desc(p);
     int begin, end, step;
     seg_range(p, begin, end, step);
     int slot = 0;
@@ -499,11 +713,11 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
     for (int i = begin; i < end && alive; i += step) {
       const Seg s = load_seg(p, i);
       const int npan = panels_in_chunk(p, s.chunk);
-      float acc[NP][32];
+      float acc[NP][CW];
 #pragma unroll
       for (int q = 0; q < NP; ++q)
 #pragma unroll
-        for (int m = 0; m < 32; ++m) acc[q][m] = 0.0f;
+        for (int m = 0; m < CW; ++m) acc[q][m] = 0.0f;
       for (int t = s.t0; t < s.t1; ++t) {
         const float ts = __ldg(p.tile_scales + t);
         int ok = 1;
@@ -514,8 +728,10 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
           if (q < npan) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_base + lane_sel + (uint32_t)slot * kSlotCols + (uint32_t)q * 32u, r);
+            uint32_t r[CW];
+            const uint32_t taddr = tmem_base + lane_sel + (uint32_t)slot * kSlotCols + (uint32_t)(q * 32 + m_first);
+            if (CW == 16) tmem_ld_32x16(taddr, reinterpret_cast<uint32_t(&)[16]>(r));
+            else tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r));
             tmem_ld_wait();
             if (q == npan - 1) {
               tc_fence_before();
@@ -523,7 +739,7 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
               if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
             }
 #pragma unroll
-            for (int m = 0; m < 32; ++m) {
+            for (int m = 0; m < CW; ++m) {
               const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
               acc[q][m] = fmaf(ts, x, acc[q][m]);
             }
@@ -539,33 +755,26 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
           const int n = n_base + q * kPanelN;
           if (n < p.N) {
             if (p.acc_out != nullptr) {
-              float* a = reinterpret_cast<float*>(p.acc_out) + (size_t)s.row * kTile * p.N + n;
+              float* a = reinterpret_cast<float*>(p.acc_out) + ((size_t)s.row * kTile + m_first) * p.N + n;
 #pragma unroll
-              for (int m = 0; m < 32; ++m) a[(size_t)m * p.N] = acc[q][m];
+              for (int m = 0; m < CW; ++m) a[(size_t)m * p.N] = acc[q][m];
             }
             const float cs = (p.col_scale != nullptr) ? __ldg(p.col_scale + n) * p.b_scale : p.b_scale;
             const float bias = (p.bias != nullptr) ? __ldg(p.bias + n) : 0.0f;
-            float v[32];
 #pragma unroll
-            for (int m = 0; m < 32; ++m) v[m] = apply_act(acc[q][m] * cs + bias, p.act);
-            store_column(p, s.row, n, v);
+            for (int c = 0; c < CW; c += 8) {
+              float v[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) v[k] = acc[q][c + k] * cs + bias;
+              store8(od, s.row, n, m_first + c, v);
+            }
           }
         }
       }
     }
+    if (threadIdx.x == 32 * kFirstEpiWarp) stamp(p, 6);
   }
-
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (abort_s) {
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) {
-    }
-    if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusTimeout);
-    __syncthreads();
-  }
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  pipeline_teardown(p, &abort_s, tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -583,15 +792,6 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
       g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   });
   return g_encode;
-}
-
-static int g_desc_variant = -1;  // debugging aid: alternative descriptor encodings
-static int desc_variant() {
-  if (g_desc_variant < 0) {
-    const char* e = getenv("VOID_B200_DESC_VARIANT");
-    g_desc_variant = e ? atoi(e) : 0;
-  }
-  return g_desc_variant;
 }
 
 struct DeviceInfo {
@@ -615,9 +815,24 @@ static DeviceInfo device_info() {
   return cache[dev];
 }
 
-template <typename K>
-static int set_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+// cudaFuncSetAttribute per (kernel, device), repeated only when a larger ring is asked for.
+// All kernels share one C++ function-pointer type, so the record is keyed by the pointer value.
+static int ensure_smem(const void* kernel, int bytes) {
+  struct Rec { const void* fn; int dev; int bytes; };
+  static Rec recs[64];
+  static int n_recs = 0;
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  Rec* r = nullptr;
+  for (int i = 0; i < n_recs; ++i)
+    if (recs[i].fn == kernel && recs[i].dev == dev) r = &recs[i];
+  if (r != nullptr && r->bytes >= bytes) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
+  if (r == nullptr && n_recs < 64) r = &recs[n_recs++];
+  if (r != nullptr) { r->fn = kernel; r->dev = dev; r->bytes = bytes; }
+  return 0;
 }
 
 static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
@@ -652,14 +867,20 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   }
   const int n_chunks = (total_panels + np - 1) / np;
   const int ctas_per_sm = drain ? 1 : (np == 4 ? 1 : 2);
-  const int stage_bytes = np * kPanelBytes + kTileBytes;
+  int group = a->tiles_per_stage;  // 0 = default
+  if (group == 0) group = (np == 1) ? 4 : 2;
+  if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
+  const int stage_bytes = group * (np * kPanelBytes + kTileBytes);
   int stages = a->stages;
   if (stages == 0) {
     const int budget = (200 * 1024) / ctas_per_sm;
     stages = budget / stage_bytes;
-    if (stages > 12) stages = 12;
+    if (stages > 8) stages = 8;
   }
-  if (stages < 2 || stages > kMaxStages) return VOID_ERR_BAD_ARG;
+  // A producer warp may run up to kProducerWarps - 1 groups ahead of the consumer's order; the
+  // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
+  // hold at least one stage per producer warp.
+  if (stages < kProducerWarps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
   const int smem_bytes = stages * stage_bytes + 1024;
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
@@ -687,17 +908,18 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.counters = a->counters;
   p.worker_partials = reinterpret_cast<int32_t*>(a->worker_partials);
   p.status = a->status;
+  p.trace = reinterpret_cast<unsigned long long*>(a->trace);
   p.np = np;
+  p.group = group;
   p.stages = stages;
+  p.use3d = (a->N % kPanelN == 0) ? 1 : 0;
   p.n_items = a->nbr * n_chunks;
 
-  // operand descriptors (see the header comment for the two shared-memory layouts)
-  uint32_t tile_lbo = 128, tile_sbo = 256, tile_layout = kLayoutNone;
-  const int variant = desc_variant();
-  if (variant & 1) { tile_lbo = 256; tile_sbo = 128; }
-  if (variant & 2) { tile_lbo = 16; tile_sbo = 256; tile_layout = kLayoutSw32; }
-  p.desc_hi_b = smem_desc_hi(tile_lbo, tile_sbo, tile_layout);
-  // one 128-byte swizzle atom along n, four 8-row groups along k, 1024 bytes apart
+  // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
+  // matrices, 128 bytes between the two k-halves (leading offset), 256 bytes between 8-row groups
+  // (stride offset).  B panel (operand A, MN-major, 128-byte swizzle): one swizzle atom along n,
+  // four 8-row groups along k, 1024 bytes apart.
+  p.desc_hi_b = smem_desc_hi(128, 256, kLayoutNone);
   p.desc_hi_a = smem_desc_hi(1024, 1024, kLayoutSw128);
   if (kind == VOID_KIND_I8) p.idesc = instr_desc(/*c s32*/ 2, /*a s8*/ 1, /*b s8*/ 1, /*a MN*/ 1, /*b K*/ 0, 128, 32);
   else p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, 1, 0, 128, 32);
@@ -713,36 +935,50 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (grid < 1) grid = 1;
   }
 
-  // B as a 2-D tensor: dim0 = n (contiguous), dim1 = k; box = one panel (128 x 32), 128-byte swizzle.
-  // Out-of-range parts of a box (n >= N, k >= K) are filled with zeros by the copy engine.
+  // B as a tensor for the copy engine, 128-byte swizzle, zero fill outside [K, N]:
+  //   3-D (N a multiple of 128): dim0 = 128 columns of a panel, dim1 = k, dim2 = panel; box 128 x 32 x np
+  //   2-D (ragged N):            dim0 = n, dim1 = k;                                      box 128 x 32
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (a->nnz > 0) {
     PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
     if (enc == nullptr) return VOID_ERR_CUDA;
-    const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->K};
-    const cuuint64_t gstride[1] = {(cuuint64_t)a->ldb};
-    const cuuint32_t box[2] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile};
-    const cuuint32_t estride[2] = {1, 1};
-    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a->b), gdim, gstride, box,
-                           estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return VOID_ERR_CUDA;
+    CUresult r = CUDA_ERROR_INVALID_VALUE;
+    if (p.use3d) {
+      const cuuint64_t gdim[3] = {(cuuint64_t)kPanelN, (cuuint64_t)a->K, (cuuint64_t)total_panels};
+      const cuuint64_t gstride[2] = {(cuuint64_t)a->ldb, (cuuint64_t)kPanelN};
+      const cuuint32_t box[3] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile, (cuuint32_t)np};
+      const cuuint32_t estride[3] = {1, 1, 1};
+      r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(a->b), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) p.use3d = 0;  // fall back to one 2-D copy per panel
+    }
+    if (!p.use3d) {
+      const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->K};
+      const cuuint64_t gstride[1] = {(cuuint64_t)a->ldb};
+      const cuuint32_t box[2] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile};
+      const cuuint32_t estride[2] = {1, 1};
+      r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a->b), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return VOID_ERR_TENSOR_MAP;
   }
 
-  cudaError_t err = cudaSuccess;
+  const int max_ring = smem_bytes;
   if (!drain) {
     if (kind == VOID_KIND_I8) {
-      if (set_smem(spmm_rowacc_kernel<VOID_KIND_I8>, smem_bytes)) return VOID_ERR_CUDA;
+      if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_I8>, max_ring)) return VOID_ERR_CUDA;
       spmm_rowacc_kernel<VOID_KIND_I8><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);
     } else {
-      if (set_smem(spmm_rowacc_kernel<VOID_KIND_F8E4M3>, smem_bytes)) return VOID_ERR_CUDA;
+      if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_F8E4M3>, max_ring)) return VOID_ERR_CUDA;
       spmm_rowacc_kernel<VOID_KIND_F8E4M3><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);
     }
   } else {
 #define VB_LAUNCH_DRAIN(KIND, NP)                                                      \
   do {                                                                                 \
-    if (set_smem(spmm_drain_kernel<KIND, NP>, smem_bytes)) return VOID_ERR_CUDA;       \
+    if (ensure_smem((const void*)spmm_drain_kernel<KIND, NP>, max_ring)) return VOID_ERR_CUDA; \
     spmm_drain_kernel<KIND, NP><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);      \
   } while (0)
     if (kind == VOID_KIND_I8) {
@@ -756,8 +992,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     }
 #undef VB_LAUNCH_DRAIN
   }
-  err = cudaGetLastError();
-  return err == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
+  return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
 }
 
 }  // namespace vb
