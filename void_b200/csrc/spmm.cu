@@ -352,6 +352,11 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
     tmem_alloc(smem_u32(tmem_base_s), tmem_cols);
     tmem_relinquish();
   }
+  // Programmatic dependent launch: the next kernel in the stream may start its own set-up while
+  // this one runs; nothing above touched global memory, everything below may, so wait here until
+  // the kernel before this one has completed and its writes are visible.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) stamp(p, 0);
   tc_fence_before();
   __syncthreads();
@@ -439,9 +444,6 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
           if (!ok) break;
           if (p.trace != nullptr && i == begin && gidx < 16) stamp(p, 16 + gidx);
           tc_fence_after();
-          const bool trc = p.trace != nullptr && i == begin && gidx == 1;
-          long long ck[6] = {0, 0, 0, 0, 0, 0};
-          if (trc) ck[0] = clock64();
           uint64_t ad = smem_desc(hi_a, sbase);
           uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
           for (int j = 0; j < gcnt; ++j) {
@@ -455,14 +457,8 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
             ad += kPanelStep * (uint64_t)np;
             bd += kTileStep;
             acc = 1u;
-            if (trc && j < 4) ck[1 + j] = clock64();
           }
           tc_commit(smem_u32(&bars.empty[stage]));
-          if (trc) {
-            ck[5] = clock64();
-            unsigned long long* tp = p.trace + (size_t)blockIdx.x * 64 + 56;
-            for (int z = 0; z < 6; ++z) tp[z] = ck[z] - ck[0];
-          }
           sbase += stage_bytes;
           if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
@@ -835,6 +831,22 @@ static int ensure_smem(const void* kernel, int bytes) {
   return 0;
 }
 
+template <typename Kernel>
+static void launch_pdl(Kernel kernel, int grid, int smem_bytes, cudaStream_t stream, const CUtensorMap& tmap,
+                       const SpmmParams& p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, tmap, p);
+}
+
 static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (a == nullptr) return VOID_ERR_BAD_ARG;
   if (a->M < 0 || a->N < 0 || a->K < 0 || a->nbr < 0 || a->nnz < 0) return VOID_ERR_BAD_ARG;
@@ -970,16 +982,16 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (!drain) {
     if (kind == VOID_KIND_I8) {
       if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_I8>, max_ring)) return VOID_ERR_CUDA;
-      spmm_rowacc_kernel<VOID_KIND_I8><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);
+      launch_pdl(spmm_rowacc_kernel<VOID_KIND_I8>, grid, smem_bytes, stream, tmap, p);
     } else {
       if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_F8E4M3>, max_ring)) return VOID_ERR_CUDA;
-      spmm_rowacc_kernel<VOID_KIND_F8E4M3><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);
+      launch_pdl(spmm_rowacc_kernel<VOID_KIND_F8E4M3>, grid, smem_bytes, stream, tmap, p);
     }
   } else {
 #define VB_LAUNCH_DRAIN(KIND, NP)                                                      \
   do {                                                                                 \
     if (ensure_smem((const void*)spmm_drain_kernel<KIND, NP>, max_ring)) return VOID_ERR_CUDA; \
-    spmm_drain_kernel<KIND, NP><<<grid, kThreads, smem_bytes, stream>>>(tmap, p);      \
+    launch_pdl(spmm_drain_kernel<KIND, NP>, grid, smem_bytes, stream, tmap, p);                \
   } while (0)
     if (kind == VOID_KIND_I8) {
       if (np == 1) VB_LAUNCH_DRAIN(VOID_KIND_I8, 1);
