@@ -219,6 +219,36 @@ typedef struct void_spmm_args {
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);
 VOID_API int void_spmm_f8(const void_spmm_args* args, void_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * void_spmm_i8 for callers that have no way to hand over scratch memory.  (This entry point has
+ * no counterpart in the reference; it exists for embedders of this library.)
+ *
+ * A planned launch with split tile rows needs device scratch: one slot of partial sums per row
+ * segment and one arrival counter per split row.  void_spmm_i8 takes them from the caller
+ * (args->partials, args->counters).  Some callers cannot provide them: a serving process whose
+ * own allocator claimed the whole GPU at start-up, so that cudaMalloc would fail; code running
+ * under a "no allocation after warm-up" rule (hard real-time loops, sandboxed plug-ins); a host
+ * language binding that can pass pointers it was given but owns no device allocator.  For them
+ * this variant uses an array that is part of the library's device image instead and allocates
+ * nothing: it calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Same arguments as void_spmm_i8 with a plan (args->segs, args->cta_seg_ptr, args->n_cta,
+ * args->panels_per_item are required); args->partials and args->counters are ignored.
+ * n_slots / n_counters are the plan's counts[1] / counts[2] (void_plan_segments).
+ *
+ * Limits: n_slots * panels_per_item * 16 KiB <= 8 MiB and n_counters <= 4096; anything larger
+ * returns VOID_ERR_TOO_LARGE.  The array costs 8 MiB + 16 KiB on every GPU that loads the
+ * library, until the process exits.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array, and it keeps the previous call's contents: the
+ * counters are cleared in stream order before each launch, partial sums are always written
+ * before they are read.  Two calls that overlap on the GPU (different streams, or different
+ * processes' threads on one device) race on it - serialise them.
+ * ------------------------------------------------------------------------------------- */
+VOID_API int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_slots, int32_t n_counters,
+                                         void_stream_t stream);
+
 /* number of SMs of the current device (grid sizing on the host side) */
 VOID_API int void_device_sm_count(void);
 

@@ -1007,9 +1007,63 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
 }
 
+// ------------------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot allocate device memory.
+// ------------------------------------------------------------------------------------------
+// Partial sums of split tile rows followed by their arrival counters.  The array lives in the
+// library's device image: every GPU that loads the library holds these bytes until the process
+// exits.
+constexpr size_t kStaticPartialsBytes = 8u << 20;    // 8 MiB of int32 partial sums
+constexpr int kStaticCounters = 4096;                // arrival counters (16 KiB)
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialsBytes + kStaticCounters * 4];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use; the address has to be asked for,
+// once per device, with that device current.
+static int static_scratch_ptr(unsigned char** out) {
+  static unsigned char* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return VOID_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return VOID_ERR_CUDA;
+    ptrs[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = ptrs[dev];
+  return VOID_OK;
+}
+
+static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_slots, int32_t n_counters, cudaStream_t stream) {
+  if (a == nullptr || n_slots < 0 || n_counters < 0) return VOID_ERR_BAD_ARG;
+  if (a->segs == nullptr || a->panels_per_item == 0) return VOID_ERR_BAD_ARG;  // a split-row plan is the point
+  const size_t slot_bytes = (size_t)a->panels_per_item * kPanelN * kTile * sizeof(int32_t);
+  if ((size_t)n_slots * slot_bytes > kStaticPartialsBytes || n_counters > kStaticCounters) return VOID_ERR_TOO_LARGE;
+  unsigned char* base = nullptr;
+  const int st = static_scratch_ptr(&base);
+  if (st != VOID_OK) return st;
+  void_spmm_args b = *a;
+  b.partials = base;
+  b.partials_bytes = (int64_t)kStaticPartialsBytes;
+  b.counters = reinterpret_cast<int32_t*>(base + kStaticPartialsBytes);
+  // The array keeps whatever the previous call left.  Partial sums are always written before they
+  // are read; the counters must start at zero (a launch that ran to the end leaves them so, a
+  // launch that gave up may not), so they are cleared in stream order before every launch.
+  if (n_counters > 0 &&
+      cudaMemsetAsync(b.counters, 0, (size_t)n_counters * sizeof(int32_t), stream) != cudaSuccess)
+    return VOID_ERR_CUDA;
+  return spmm_launch(&b, VOID_KIND_I8, stream);
+}
+
 }  // namespace vb
 
 extern "C" {
+
+int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_slots, int32_t n_counters,
+                                void_stream_t stream) {
+  return vb::spmm_i8_static_scratch(args, n_slots, n_counters, reinterpret_cast<cudaStream_t>(stream));
+}
 
 int void_spmm_i8(const void_spmm_args* args, void_stream_t stream) {
   return vb::spmm_launch(args, VOID_KIND_I8, reinterpret_cast<cudaStream_t>(stream));
