@@ -192,7 +192,7 @@ __global__ void quant_fp8_tiles_kernel(const float4* __restrict__ values, int64_
 
 // column absmax of a row-major [K, N] matrix: block = 128 columns x a slab of k rows
 constexpr int kColBlock = 128;
-constexpr int kRowSlab = 256;
+constexpr int kRowSlab = 64;
 __global__ void col_amax_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, float* __restrict__ amax) {
   const int n = blockIdx.x * kColBlock + threadIdx.x;
   if (n >= N) return;
@@ -228,7 +228,33 @@ __global__ void quant_cols_kernel(const float* __restrict__ b, int64_t ldb, int 
   }
   q[(size_t)k * ldq + n] = o;
 }
-
+// four columns per thread (float4 in, 4 bytes out); needs N, ldb, ldq multiples of 4 and aligned rows
+__global__ void quant_cols4_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, int kind,
+                                   uint8_t* __restrict__ q, int64_t ldq, const float* __restrict__ scale,
+                                   int scale_stride) {
+  const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int k = blockIdx.y;
+  if (n >= ldq) return;
+  uchar4 o = make_uchar4(0, 0, 0, 0);
+  if (n < N) {
+    const float4 x = *reinterpret_cast<const float4*>(b + (size_t)k * ldb + n);
+    float s0, s1, s2, s3;
+    if (scale_stride) {
+      const float4 s = *reinterpret_cast<const float4*>(scale + n);
+      s0 = s.x; s1 = s.y; s2 = s.z; s3 = s.w;
+    } else {
+      s0 = s1 = s2 = s3 = scale[0];
+    }
+    if (kind == VOID_KIND_I8) {
+      o.x = (uint8_t)quant_i8(x.x, s0); o.y = (uint8_t)quant_i8(x.y, s1);
+      o.z = (uint8_t)quant_i8(x.z, s2); o.w = (uint8_t)quant_i8(x.w, s3);
+    } else {
+      o.x = quant_e4m3(x.x, __fdiv_rn(1.0f, s0)); o.y = quant_e4m3(x.y, __fdiv_rn(1.0f, s1));
+      o.z = quant_e4m3(x.z, __fdiv_rn(1.0f, s2)); o.w = quant_e4m3(x.w, __fdiv_rn(1.0f, s3));
+    }
+  }
+  *reinterpret_cast<uchar4*>(q + (size_t)k * ldq + n) = o;
+}
 // absmax of a whole row-major [K, N] matrix into amax[0] (zero before the launch)
 __global__ void tensor_amax_kernel(const float* __restrict__ b, int64_t ldb, int K, int N, float* __restrict__ amax) {
   const int n = blockIdx.x * kColBlock + threadIdx.x;
@@ -375,12 +401,20 @@ int void_quant_fp8_tiles(const float* values, int64_t nnz, uint8_t* q, float* sc
 
 static void quant_pass(const float* b, int64_t ldb, int K, int N, int kind, void* q, int64_t ldq, const float* scale,
                        int scale_stride, cudaStream_t st) {
+  const bool vec4 = (N % 4 == 0) && (ldb % 4 == 0) && (ldq % 4 == 0) && ((reinterpret_cast<uintptr_t>(b) & 15u) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(q) & 3u) == 0) && ((reinterpret_cast<uintptr_t>(scale) & 15u) == 0);
   // blockIdx.y is limited to 65535: quantise in slabs of rows
   for (int k0 = 0; k0 < K; k0 += 65535) {
     const int kk = (K - k0) < 65535 ? (K - k0) : 65535;
-    dim3 g2((unsigned)((ldq + 255) / 256), kk);
-    quant_cols_kernel<<<g2, 256, 0, st>>>(b + (size_t)k0 * ldb, ldb, kk, N, kind,
-                                          reinterpret_cast<uint8_t*>(q) + (size_t)k0 * ldq, ldq, scale, scale_stride);
+    const float* src = b + (size_t)k0 * ldb;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(q) + (size_t)k0 * ldq;
+    if (vec4) {
+      dim3 g2((unsigned)((ldq / 4 + 127) / 128), kk);
+      quant_cols4_kernel<<<g2, 128, 0, st>>>(src, ldb, kk, N, kind, dst, ldq, scale, scale_stride);
+    } else {
+      dim3 g2((unsigned)((ldq + 255) / 256), kk);
+      quant_cols_kernel<<<g2, 256, 0, st>>>(src, ldb, kk, N, kind, dst, ldq, scale, scale_stride);
+    }
   }
 }
 

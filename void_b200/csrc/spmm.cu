@@ -136,11 +136,13 @@ __device__ __forceinline__ int panels_in_chunk(const SpmmParams& p, int chunk) {
   return left < p.np ? left : p.np;
 }
 
-// GELU in the tanh form written with a sigmoid, void/fusion.py:38-43.
+// GELU in the tanh form written with a sigmoid, void/fusion.py:38-43.  exp and the reciprocal use
+// the hardware approximations (a few ulp; far inside the path's 1e-3 bar): with the full-precision
+// versions this epilogue, run by two warps per scheduler, cost more than the product itself.
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh_sigmoid(float x) {
   const float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
-  const float sig = 1.0f / (1.0f + expf(-2.0f * inner));
-  const float t = 2.0f * sig - 1.0f;
+  const float t = 2.0f * fast_sigmoid(2.0f * inner) - 1.0f;
   return x * 0.5f * (1.0f + t);
 }
 // What an epilogue thread needs to know about C, read from the kernel parameters once.
@@ -171,7 +173,7 @@ __device__ __forceinline__ void store8(const OutDesc& o, int row, int n, int m0,
       break;
     case VOID_ACT_SILU:
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = v[k] * (1.0f / (1.0f + expf(-v[k])));
+      for (int k = 0; k < 8; ++k) v[k] = v[k] * fast_sigmoid(v[k]);
       break;
     default:
       break;
@@ -231,7 +233,7 @@ __device__ __forceinline__ void finish_cols(const OutDesc& o, int row, int n, in
     for (int k = 0; k < kColsPerWarp; ++k) {
       if (o.act == VOID_ACT_GELU) v[k] = gelu_tanh_sigmoid(v[k]);
       else if (o.act == VOID_ACT_RELU) v[k] = fmaxf(v[k], 0.0f);
-      else v[k] = v[k] * (1.0f / (1.0f + expf(-v[k])));
+      else v[k] = v[k] * fast_sigmoid(v[k]);
     }
   }
   const int r0 = row * kTile + m0;
@@ -279,8 +281,11 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
   seg_range(p, begin, end, step);
   const int G = p.group;
   int g = 0;  // groups of all earlier segments
+  Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
+  if (begin < end) seg_next = load_seg(p, begin);
   for (int i = begin; i < end; i += step) {
-    const Seg s = load_seg(p, i);
+    const Seg s = seg_next;
+    if (i + step < end) seg_next = load_seg(p, i + step);
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
     const uint32_t unit_bytes = (uint32_t)(kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes);
@@ -427,8 +432,11 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
       uint32_t sbase = ring_base;
       uint32_t it = 0;
       bool ok = true;
+      Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
+      if (begin < end) seg_next = load_seg(p, begin);
       for (int i = begin; i < end && ok; i += step, ++it) {
-        const Seg s = load_seg(p, i);
+        const Seg s = seg_next;
+        if (i + step < end) seg_next = load_seg(p, i + step);
         const int npan = panels_in_chunk(p, s.chunk);
         const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
         ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, abort_flag);
@@ -482,8 +490,11 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
     int begin, end, step;
     seg_range(p, begin, end, step);
     uint32_t it = 0;
+    Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
+    if (begin < end) seg_next = load_seg(p, begin);
     for (int i = begin; i < end; i += step, ++it) {
-      const Seg s = load_seg(p, i);
+      const Seg s = seg_next;
+      if (i + step < end) seg_next = load_seg(p, i + step);
       const int npan = panels_in_chunk(p, s.chunk);
       const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
       const bool has = s.t1 > s.t0;
@@ -631,18 +642,22 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
-  constexpr uint32_t kSlotCols = NP * 32;
+  // Tensor memory is cut into slot groups: one group receives the products of the tiles of one ring
+  // stage (up to p.group tiles, NP panels each), so that MMA warp and epilogue hand over once per
+  // stage, not once per tile.
+  constexpr uint32_t kTileCols = NP * 32;   // TMEM columns of one tile's product
   constexpr uint32_t kTmemCols = 512;
-  constexpr int kSlots = (kTmemCols / kSlotCols) < kMaxSlots ? (kTmemCols / kSlotCols) : kMaxSlots;
   constexpr int CW = kColsPerWarp;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t stage_bytes = (uint32_t)(p.group * (NP * kPanelBytes + kTileBytes));
+  const uint32_t group_cols = (uint32_t)p.group * kTileCols;
+  const int n_slots = (int)(kTmemCols / group_cols);   // >= 2: checked at launch
   volatile int* abort_flag = &abort_s;
 
-  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, kSlots, kTmemCols);
+  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < kProducerWarps) {
@@ -661,33 +676,37 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
       uint32_t phase = 0, sphase = 0;
       uint32_t sbase = ring_base;
       bool ok = true;
+      Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
+      if (begin < end) seg_next = load_seg(p, begin);
       for (int i = begin; i < end && ok; i += step) {
-        const Seg s = load_seg(p, i);
+        const Seg s = seg_next;
+        if (i + step < end) seg_next = load_seg(p, i + step);
         const int npan = panels_in_chunk(p, s.chunk);
-        for (int t = s.t0; t < s.t1 && ok; t += G) {
+        for (int t = s.t0; t < s.t1; t += G) {
           const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
           ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
           if (!ok) break;
+          ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
           uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
+          uint32_t d = tmem_base + (uint32_t)slot * group_cols;
           for (int j = 0; j < gcnt; ++j) {
-            ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
             uint64_t adq = ad;
-            uint32_t d = tmem_base + (uint32_t)slot * kSlotCols;
+            uint32_t dq = d;
             for (int q = 0; q < npan; ++q) {
-              issue_mma<KIND>(d, adq, bd, idesc, 0u);
+              issue_mma<KIND>(dq, adq, bd, idesc, 0u);
               adq += kPanelStep;
-              d += 32u;
+              dq += 32u;
             }
-            tc_commit(smem_u32(&bars.acc_full[slot]));
             ad += kPanelStep * (uint64_t)NP;
             bd += kTileStep;
-            if (++slot == kSlots) { slot = 0; sphase ^= 1u; }
+            d += kTileCols;
           }
-          if (!ok) break;
+          tc_commit(smem_u32(&bars.acc_full[slot]));
           tc_commit(smem_u32(&bars.empty[stage]));
+          if (++slot == n_slots) { slot = 0; sphase ^= 1u; }
           sbase += stage_bytes;
           if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
@@ -701,47 +720,57 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
     const int m_first = half * CW;
     const OutDesc od = out_desc(p);
+    const int G = p.group;
     int begin, end, step;
     seg_range(p, begin, end, step);
     int slot = 0;
     uint32_t sphase = 0;
     bool alive = true;
+    Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
+    if (begin < end) seg_next = load_seg(p, begin);
     for (int i = begin; i < end && alive; i += step) {
-      const Seg s = load_seg(p, i);
+      const Seg s = seg_next;
+      if (i + step < end) seg_next = load_seg(p, i + step);
       const int npan = panels_in_chunk(p, s.chunk);
       float acc[NP][CW];
 #pragma unroll
       for (int q = 0; q < NP; ++q)
 #pragma unroll
         for (int m = 0; m < CW; ++m) acc[q][m] = 0.0f;
-      for (int t = s.t0; t < s.t1; ++t) {
-        const float ts = __ldg(p.tile_scales + t);
+      for (int t = s.t0; t < s.t1; t += G) {
+        const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
+        // scale of lane j's tile, fetched before the products are ready
+        const float my_ts = (lane < gcnt) ? __ldg(p.tile_scales + t + lane) : 0.0f;
         int ok = 1;
         if (lane == 0) ok = mbar_wait(smem_u32(&bars.acc_full[slot]), sphase, abort_flag) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) { alive = false; break; }
         tc_fence_after();
+        for (int j = 0; j < gcnt; ++j) {
+          const float ts = __shfl_sync(0xffffffffu, my_ts, j);
+          const uint32_t tile_addr = tmem_base + lane_sel + (uint32_t)slot * group_cols + (uint32_t)j * kTileCols +
+                                     (uint32_t)m_first;
 #pragma unroll
-        for (int q = 0; q < NP; ++q) {
-          if (q < npan) {
-            uint32_t r[CW];
-            const uint32_t taddr = tmem_base + lane_sel + (uint32_t)slot * kSlotCols + (uint32_t)(q * 32 + m_first);
-            if (CW == 16) tmem_ld_32x16(taddr, reinterpret_cast<uint32_t(&)[16]>(r));
-            else tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r));
-            tmem_ld_wait();
-            if (q == npan - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
-            }
+          for (int q = 0; q < NP; ++q) {
+            if (q < npan) {
+              uint32_t r[CW];
+              if (CW == 16) tmem_ld_32x16(tile_addr + (uint32_t)q * 32u, reinterpret_cast<uint32_t(&)[16]>(r));
+              else tmem_ld_32x32(tile_addr + (uint32_t)q * 32u, reinterpret_cast<uint32_t(&)[32]>(r));
+              tmem_ld_wait();
+              if (j == gcnt - 1 && q == npan - 1) {  // this warp has read the whole slot group
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
+              }
 #pragma unroll
-            for (int m = 0; m < CW; ++m) {
-              const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
-              acc[q][m] = fmaf(ts, x, acc[q][m]);
+              for (int m = 0; m < CW; ++m) {
+                const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
+                acc[q][m] = fmaf(ts, x, acc[q][m]);
+              }
             }
           }
         }
-        if (++slot == kSlots) { slot = 0; sphase ^= 1u; }
+        if (++slot == n_slots) { slot = 0; sphase ^= 1u; }
       }
       if (!alive) break;
       const int n_base = s.chunk * NP * kPanelN + quad * 32 + lane;
@@ -882,6 +911,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   int group = a->tiles_per_stage;  // 0 = default
   if (group == 0) group = (np == 1) ? 4 : 2;
   if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
+  if (drain && group * np * 32 * 2 > 512) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
   const int stage_bytes = group * (np * kPanelBytes + kTileBytes);
   int stages = a->stages;
   if (stages == 0) {
