@@ -149,19 +149,22 @@ VOID_API int void_streamk_table(const int32_t* row_ptr, int32_t nbr, int64_t nnz
 VOID_API int64_t void_plan_capacity(int64_t nnz, int32_t nbr, int32_t n_chunks, int32_t n_cta,
                                     int32_t split_rows, int32_t chunk_tiles);
 VOID_API size_t void_plan_ws_bytes(int32_t nbr, int32_t n_cta);
-/* chunk_tiles: chunk length of the worker table (void_streamk_target), used when split_rows > 0.
+/* row_cost (>= 1): what finishing one (tile row, column chunk) costs relative to one tile of work; it
+ * weights the shares so that a CTA handed many short rows is not handed many tiles as well.
+ * chunk_tiles: chunk length of the worker table (void_streamk_target), used when split_rows > 0.
  * woff: (nbr + 1) workers-before-row prefix left in the ws of void_streamk_table, needed for
  * split_rows = 2 only.  ws: device scratch of void_plan_ws_bytes(nbr, n_cta) bytes.          */
 VOID_API int void_plan_segments(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, int32_t n_cta,
-                                int32_t split_rows, int32_t chunk_tiles, const int32_t* woff,
-                                int32_t* segs, int64_t segs_capacity, int32_t* cta_seg_ptr,
-                                int32_t* counts, void* ws, size_t ws_bytes, void_stream_t stream);
+                                int32_t split_rows, int32_t chunk_tiles, int32_t row_cost,
+                                const int32_t* woff, int32_t* segs, int64_t segs_capacity,
+                                int32_t* cta_seg_ptr, int32_t* counts, void* ws, size_t ws_bytes,
+                                void_stream_t stream);
 /* The same splitting arithmetic over HOST arrays, run as plain loops on the CPU.  It exists so
  * that the splitter can be tested on machines without a GPU; the SpMM path never calls it.   */
 VOID_API int void_plan_segments_host(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks,
                                      int32_t n_cta, int32_t split_rows, int32_t chunk_tiles,
-                                     const int32_t* woff, int32_t* segs, int64_t segs_capacity,
-                                     int32_t* cta_seg_ptr, int32_t* counts);
+                                     int32_t row_cost, const int32_t* woff, int32_t* segs,
+                                     int64_t segs_capacity, int32_t* cta_seg_ptr, int32_t* counts);
 
 /* ---------------------------------------------------------------------------------------
  * SpMM  C = act(dequant(A_q . B_q) + bias).

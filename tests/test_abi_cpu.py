@@ -65,7 +65,7 @@ def test_streamk_target_matches_reference_formula():
     assert lib.void_streamk_target(0, -1, 16) == 0
 
 
-def _plan(row_ptr, n_chunks, n_cta, mode, T):
+def _plan(row_ptr, n_chunks, n_cta, mode, T, row_cost=1):
     lib = _lib.load()
     nbr = len(row_ptr) - 1
     nnz = int(row_ptr[-1])
@@ -77,15 +77,15 @@ def _plan(row_ptr, n_chunks, n_cta, mode, T):
     if mode == 2:
         cnt = np.diff(row_ptr)
         woff = np.concatenate([[0], np.cumsum((cnt + T - 1) // T)]).astype(np.int32)
-    st = lib.void_plan_segments_host(row_ptr.ctypes.data, nbr, n_chunks, n_cta, mode, T,
+    st = lib.void_plan_segments_host(row_ptr.ctypes.data, nbr, n_chunks, n_cta, mode, T, row_cost,
                                      None if woff is None else woff.ctypes.data, segs.ctypes.data, cap,
                                      cptr.ctypes.data, counts.ctypes.data)
     assert st == 0 and counts[3] == 0
     return segs[:counts[0]], cptr, counts
 
 
-def _check_plan(row_ptr, n_chunks, n_cta, mode, T):
-    segs, cptr, counts = _plan(row_ptr, n_chunks, n_cta, mode, T)
+def _check_plan(row_ptr, n_chunks, n_cta, mode, T, row_cost=1):
+    segs, cptr, counts = _plan(row_ptr, n_chunks, n_cta, mode, T, row_cost)
     nbr = len(row_ptr) - 1
     assert cptr[0] == 0 and cptr[-1] == len(segs) and (np.diff(cptr) >= 0).all()
     rows = {}
@@ -128,7 +128,8 @@ def test_plan_invariants_random():
         if row_ptr[-1] == 0:
             continue
         for mode in (0, 1, 2):
-            _check_plan(row_ptr, int(rng.integers(1, 4)), int(rng.integers(1, 300)), mode, int(rng.integers(1, 17)))
+            _check_plan(row_ptr, int(rng.integers(1, 4)), int(rng.integers(1, 300)), mode, int(rng.integers(1, 17)),
+                        int(rng.integers(1, 12)))
 
 
 def test_plan_splits_heavy_rows_only_when_asked():

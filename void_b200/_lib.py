@@ -58,8 +58,8 @@ _PROTOTYPES = {
     "void_streamk_table": (ctypes.c_int, [c_vp, c_i32, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "void_plan_capacity": (c_i64, [c_i64, c_i32, c_i32, c_i32, c_i32, c_i32]),
     "void_plan_ws_bytes": (c_sz, [c_i32, c_i32]),
-    "void_plan_segments": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp]),
-    "void_plan_segments_host": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "void_plan_segments": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "void_plan_segments_host": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "void_spmm_i8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
     "void_spmm_f8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
     "void_spmm_i8_static_scratch": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_i32, c_i32, c_vp]),

@@ -130,8 +130,11 @@ def streamk_table(row_ptr: torch.Tensor, nbr: int, nnz: int, n_workers: Optional
     return rows[:n], start[:n], end[:n], atomic[:n].to(torch.bool), woff, target
 
 
+ROW_COST = 6   # epilogue of one (tile row, chunk) in units of one tile's work, measured on B200
+
+
 def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chunk_tiles: int = 0,
-              woff: Optional[torch.Tensor] = None) -> Plan:
+              woff: Optional[torch.Tensor] = None, row_cost: int = ROW_COST) -> Plan:
     """Cut the tile stream of ``packed`` into ``n_cta`` shares on the device (void_plan_segments)."""
     lib = _lib.load()
     dev = packed.row_ptr.device
@@ -145,7 +148,7 @@ def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chun
         ws_bytes = lib.void_plan_ws_bytes(packed.nbr, n_cta)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         _lib.check(lib.void_plan_segments(_lib.ptr(packed.row_ptr), packed.nbr, n_chunks, n_cta, mode, chunk_tiles,
-                                          _lib.ptr(woff), _lib.ptr(segs), cap, _lib.ptr(cta_seg_ptr), _lib.ptr(counts),
+                                          row_cost, _lib.ptr(woff), _lib.ptr(segs), cap, _lib.ptr(cta_seg_ptr), _lib.ptr(counts),
                                           _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev)), "void_plan_segments")
         n_segs, n_slots, n_ctr, overflow = (int(x) for x in counts.tolist())
         if overflow:

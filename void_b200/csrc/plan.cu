@@ -1,13 +1,14 @@
 // Device-side work splitter of the SpMM kernels.
 //
 // The work of one launch is the sequence of "virtual rows" v = (column chunk c, tile row r),
-// v = c * nbr + r, each worth (tiles in row r) + 1 units (the +1 stands for the epilogue, so
-// that empty rows, which still have to be written as zeros, cost something).  Because
-// row_ptr is already a prefix sum, the start position of a virtual row on that axis is
-// closed-form:  P(v) = c * (nnz + nbr) + row_ptr[r] + r.  The axis is cut into n_cta shares of
+// v = c * nbr + r, each worth (tiles in row r) + row_cost units.  row_cost stands for the epilogue:
+// reading the accumulator back, dequantising, activating and storing 32 x chunk columns costs as
+// much as several tiles of products, and empty rows still have to be written as zeros.  Because
+// row_ptr is already a prefix sum, the start position of a virtual row on that axis is closed-form:
+// P(v) = c * (nnz + row_cost * nbr) + row_ptr[r] + row_cost * r.  The axis is cut into n_cta shares of
 // equal length; cut k lands inside some row and is then moved
-//   mode 0  to the next tile-row boundary (rows are never split),
-//   mode 1  to the next tile-row boundary if the row is light, else to the nearest multiple of
+//   mode 0  to the nearer tile-row boundary (rows are never split),
+//   mode 1  to the nearer tile-row boundary if the row is light, else to the nearest multiple of
 //           `chunk_tiles` inside the row (the chunk boundaries of the Stream-K worker table,
 //           void/stream_k.py:84-97), so that a heavy row is shared by several CTAs,
 //   mode 2  always to the nearest chunk boundary, and every chunk becomes a segment of its
@@ -30,6 +31,7 @@ struct PlanIn {
   const int32_t* row_ptr;
   const int32_t* woff;  // mode 2: workers before each row (nbr + 1), else null
   int nbr, n_chunks, n_cta, mode, chunk_tiles;
+  int row_cost;  // what finishing one (tile row, chunk) costs, in units of one tile's work
 };
 
 struct PlanWs {       // all arrays have n_cta + 2 entries
@@ -49,8 +51,9 @@ __host__ __device__ inline int row_cnt(const PlanIn& in, int v) {
 
 // phase 1: boundary j in [0, n_cta]
 __host__ __device__ inline void plan_boundary(const PlanIn& in, const PlanWs& ws, int j) {
+  const long long c0 = in.row_cost;
   const long long nnz = in.row_ptr[in.nbr];
-  const long long wrow = nnz + in.nbr;
+  const long long wrow = nnz + c0 * in.nbr;
   const long long W = wrow * in.n_chunks;
   const int V = in.nbr * in.n_chunks;
   if (j >= in.n_cta) {
@@ -61,26 +64,28 @@ __host__ __device__ inline void plan_boundary(const PlanIn& in, const PlanWs& ws
   const long long x = (W * j) / in.n_cta;
   const int c = (int)(x / wrow);
   const long long y = x - (long long)c * wrow;
-  int lo = 0, hi = in.nbr - 1;  // largest r with row_ptr[r] + r <= y
+  int lo = 0, hi = in.nbr - 1;  // largest r with row_ptr[r] + c0 * r <= y
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
-    if ((long long)in.row_ptr[mid] + mid <= y) lo = mid;
+    if ((long long)in.row_ptr[mid] + c0 * mid <= y) lo = mid;
     else hi = mid - 1;
   }
   const int r = lo;
-  const int d = (int)(y - ((long long)in.row_ptr[r] + r));  // 0 .. cnt
+  const long long d = y - ((long long)in.row_ptr[r] + c0 * r);  // 0 .. cnt + c0 - 1
   const int cnt = in.row_ptr[r + 1] - in.row_ptr[r];
   int v = c * in.nbr + r, o = 0;
   const long long share = W / in.n_cta;
-  const bool splittable = in.chunk_tiles > 0 && (in.mode == 2 || (in.mode == 1 && (long long)cnt + 1 > share));
+  const bool splittable = in.chunk_tiles > 0 && cnt > 0 &&
+                          (in.mode == 2 || (in.mode == 1 && (long long)cnt + c0 > share));
   if (d == 0) {
     o = 0;
   } else if (!splittable) {
-    v += 1;
+    if (2 * d >= (long long)cnt + c0) v += 1;  // nearer end of the row
     o = 0;
   } else {
     const int T = in.chunk_tiles;
-    o = ((d - 1 + T / 2) / T) * T;
+    const long long tile = d > c0 ? d - c0 : 0;  // the row's own cost comes first on the axis
+    o = (int)(((tile + T / 2) / T) * T);
     if (o >= cnt) { v += 1; o = 0; }
   }
   ws.bv[j] = v;
@@ -298,12 +303,14 @@ static int plan_check(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, int
 }
 
 int void_plan_segments(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, int32_t n_cta, int32_t split_rows,
-                       int32_t chunk_tiles, const int32_t* woff, int32_t* segs, int64_t segs_capacity,
-                       int32_t* cta_seg_ptr, int32_t* counts, void* ws, size_t ws_bytes, void_stream_t stream) {
+                       int32_t chunk_tiles, int32_t row_cost, const int32_t* woff, int32_t* segs,
+                       int64_t segs_capacity, int32_t* cta_seg_ptr, int32_t* counts, void* ws, size_t ws_bytes,
+                       void_stream_t stream) {
   const int st = plan_check(row_ptr, nbr, n_chunks, n_cta, split_rows, chunk_tiles, woff, segs, cta_seg_ptr, counts);
   if (st != VOID_OK) return st;
   if (ws == nullptr || ws_bytes < void_plan_ws_bytes(nbr, n_cta)) return VOID_ERR_WORKSPACE;
-  PlanIn in{row_ptr, woff, nbr, n_chunks, n_cta, split_rows, chunk_tiles};
+  if (row_cost < 1) return VOID_ERR_BAD_ARG;
+  PlanIn in{row_ptr, woff, nbr, n_chunks, n_cta, split_rows, chunk_tiles, row_cost};
   const PlanWs w = carve_ws(reinterpret_cast<int32_t*>(ws), n_cta);
   plan_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(in, w, segs, segs_capacity, cta_seg_ptr, counts);
   return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
@@ -313,12 +320,13 @@ int void_plan_segments(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, in
 // loops.  It exists so that the splitter can be tested where there is no GPU; nothing in the
 // SpMM path calls it.
 int void_plan_segments_host(const int32_t* row_ptr, int32_t nbr, int32_t n_chunks, int32_t n_cta,
-                            int32_t split_rows, int32_t chunk_tiles, const int32_t* woff, int32_t* segs,
-                            int64_t segs_capacity, int32_t* cta_seg_ptr, int32_t* counts) {
+                            int32_t split_rows, int32_t chunk_tiles, int32_t row_cost, const int32_t* woff,
+                            int32_t* segs, int64_t segs_capacity, int32_t* cta_seg_ptr, int32_t* counts) {
   const int st = plan_check(row_ptr, nbr, n_chunks, n_cta, split_rows, chunk_tiles, woff, segs, cta_seg_ptr, counts);
   if (st != VOID_OK) return st;
   std::vector<int32_t> buf(7 * ((size_t)n_cta + 2), 0);
-  PlanIn in{row_ptr, woff, nbr, n_chunks, n_cta, split_rows, chunk_tiles};
+  if (row_cost < 1) return VOID_ERR_BAD_ARG;
+  PlanIn in{row_ptr, woff, nbr, n_chunks, n_cta, split_rows, chunk_tiles, row_cost};
   const PlanWs w = carve_ws(buf.data(), n_cta);
   const int G = n_cta;
   for (int j = 0; j <= G; ++j) plan_boundary(in, w, j);

@@ -86,6 +86,7 @@ struct SpmmParams {
   int group;    // tiles per ring stage
   int stages;   // ring depth
   int use3d;    // B panels of a tile fetched by one 3-D TMA
+  int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
   int n_items;  // without a plan: nbr * n_chunks
   unsigned long long desc_hi_a;  // B panel  (instruction operand A: MN-major, 128B swizzle)
   unsigned long long desc_hi_b;  // A tile   (instruction operand B: K-major, no swizzle)
@@ -141,9 +142,9 @@ __device__ __forceinline__ int panels_in_chunk(const SpmmParams& p, int chunk) {
 // versions this epilogue, run by two warps per scheduler, cost more than the product itself.
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh_sigmoid(float x) {
-  const float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
-  const float t = 2.0f * fast_sigmoid(2.0f * inner) - 1.0f;
-  return x * 0.5f * (1.0f + t);
+  // x * 0.5 * (1 + (2 sigmoid(2u) - 1)) = x * sigmoid(2u),  2u = 1.5957691216 (x + 0.044715 x^3)
+  const float two_u = 1.5957691216f * x * fmaf(0.044715f * x, x, 1.0f);
+  return x * fast_sigmoid(two_u);
 }
 // What an epilogue thread needs to know about C, read from the kernel parameters once.
 struct OutDesc {
@@ -646,7 +647,7 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
   // stage (up to p.group tiles, NP panels each), so that MMA warp and epilogue hand over once per
   // stage, not once per tile.
   constexpr uint32_t kTileCols = NP * 32;   // TMEM columns of one tile's product
-  constexpr uint32_t kTmemCols = 512;
+  const uint32_t kTmemCols = (uint32_t)p.tmem_cols;
   constexpr int CW = kColsPerWarp;
 
   const int warp = threadIdx.x >> 5;
@@ -907,11 +908,12 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     }
   }
   const int n_chunks = (total_panels + np - 1) / np;
-  const int ctas_per_sm = drain ? 1 : (np == 4 ? 1 : 2);
+  const int ctas_per_sm = (np == 4) ? 1 : 2;
   int group = a->tiles_per_stage;  // 0 = default
   if (group == 0) group = (np == 1) ? 4 : 2;
   if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
-  if (drain && group * np * 32 * 2 > 512) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
+  const int drain_tmem = 512 / ctas_per_sm;
+  if (drain && group * np * 32 * 2 > drain_tmem) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
   const int stage_bytes = group * (np * kPanelBytes + kTileBytes);
   int stages = a->stages;
   if (stages == 0) {
@@ -955,6 +957,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.group = group;
   p.stages = stages;
   p.use3d = (a->N % kPanelN == 0) ? 1 : 0;
+  p.tmem_cols = drain_tmem;
   p.n_items = a->nbr * n_chunks;
 
   // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
