@@ -136,7 +136,8 @@ VOID_API int void_quant_i8_tensor(const float* b, int64_t ldb, int32_t K, int32_
  * row; with split_rows = 2 every worker of the table becomes a segment of its own.
  * Output: segs (8 int32 each: row, n_chunk, t0, t1, nseg, slot0, my_idx, counter),
  * cta_seg_ptr[n_cta+1], counts[4] = {n_segs, n_slots, n_counters, overflow flag}; segs needs
- * void_plan_capacity(...) entries.
+ * void_plan_capacity(...) entries.  n_counters is the number of split rows: each needs one
+ * counter and one int32 accumulator of panels_per_item * 128 * 32 entries (void_spmm_args).
  * ------------------------------------------------------------------------------------- */
 VOID_API int64_t void_streamk_table_capacity(int64_t nnz, int32_t nbr);
 /* chunk length ("target_work") of the table: void/stream_k.py:61-67; 0 when nnz == 0 */
@@ -204,7 +205,8 @@ typedef struct void_spmm_args {
   const int32_t* segs;
   const int32_t* cta_seg_ptr;
   int32_t n_cta;             /* CTAs the plan was made for; 0 without a plan             */
-  void* partials;            /* n_slots * 32 * chunk_cols * 4 bytes, split rows only     */
+  void* partials;            /* n_counters * panels_per_item * 16 KiB of int32 row
+                                accumulators, ZERO before the first use; left zero again */
   int64_t partials_bytes;
   int32_t* counters;         /* [n_counters] zero before the first use; left zero again  */
   void* worker_partials;     /* optional [n_segs, 32, N] int32: every segment's own sum  */
@@ -226,30 +228,30 @@ VOID_API int void_spmm_f8(const void_spmm_args* args, void_stream_t stream);
  * void_spmm_i8 for callers that have no way to hand over scratch memory.  (This entry point has
  * no counterpart in the reference; it exists for embedders of this library.)
  *
- * A planned launch with split tile rows needs device scratch: one slot of partial sums per row
- * segment and one arrival counter per split row.  void_spmm_i8 takes them from the caller
- * (args->partials, args->counters).  Some callers cannot provide them: a serving process whose
- * own allocator claimed the whole GPU at start-up, so that cudaMalloc would fail; code running
- * under a "no allocation after warm-up" rule (hard real-time loops, sandboxed plug-ins); a host
- * language binding that can pass pointers it was given but owns no device allocator.  For them
- * this variant uses an array that is part of the library's device image instead and allocates
- * nothing: it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * A planned launch with split tile rows needs device scratch: one int32 accumulator and one
+ * arrival counter per split row.  void_spmm_i8 takes them from the caller (args->partials,
+ * args->counters).  Some callers cannot provide them: a serving process whose own allocator
+ * claimed the whole GPU at start-up, so that cudaMalloc would fail; code running under a "no
+ * allocation after warm-up" rule (hard real-time loops, sandboxed plug-ins); a host language
+ * binding that can pass pointers it was given but owns no device allocator.  For them this variant
+ * uses an array that is part of the library's device image instead and allocates nothing: it
+ * calls no cudaMalloc / cudaFree and no allocating library routine.
  *
  * Same arguments as void_spmm_i8 with a plan (args->segs, args->cta_seg_ptr, args->n_cta,
  * args->panels_per_item are required); args->partials and args->counters are ignored.
- * n_slots / n_counters are the plan's counts[1] / counts[2] (void_plan_segments).
+ * n_split_rows is the plan's counts[2] (void_plan_segments).
  *
- * Limits: n_slots * panels_per_item * 16 KiB <= 8 MiB and n_counters <= 4096; anything larger
- * returns VOID_ERR_TOO_LARGE.  The array costs 8 MiB + 16 KiB on every GPU that loads the
+ * Limits: n_split_rows * panels_per_item * 16 KiB <= 8 MiB and n_split_rows <= 4096; anything
+ * larger returns VOID_ERR_TOO_LARGE.  The array costs 8 MiB + 16 KiB on every GPU that loads the
  * library, until the process exits.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current); make that first call outside any stream capture.
- * All calls on a device share the one array, and it keeps the previous call's contents: the
- * counters are cleared in stream order before each launch, partial sums are always written
- * before they are read.  Two calls that overlap on the GPU (different streams, or different
- * processes' threads on one device) race on it - serialise them.
+ * All calls on a device share the one array, and it keeps the previous call's contents: the part
+ * a call uses (accumulators and counters) is cleared in stream order before its launch.  Two
+ * calls that overlap on the GPU (different streams, or different host threads on one device)
+ * race on it - serialise them.
  * ------------------------------------------------------------------------------------- */
-VOID_API int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_slots, int32_t n_counters,
+VOID_API int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_split_rows,
                                          void_stream_t stream);
 
 /* number of SMs of the current device (grid sizing on the host side) */

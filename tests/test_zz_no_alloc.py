@@ -3,14 +3,14 @@
 Who needs it: an embedder that cannot give the library scratch memory - for example a serving
 process whose allocator took the whole GPU at start-up (cudaMalloc fails from then on), a loop
 that must not allocate after warm-up, or a foreign-language binding that owns no device
-allocator.  For those callers the split-row SpMM parks its partial sums in an array built into
-the library instead of in caller memory.
+allocator.  For those callers the split-row SpMM keeps the int32 accumulators of split rows in an
+array built into the library instead of in caller memory.
 
 The test drives the entry point straight through the C ABI, twice in a row on the same inputs,
 and requires the result to be bit-identical to what the ordinary entry point (caller-provided
 scratch) produces: the partial sums are integers, so there is no tolerance to grant.  The second
-call checks that nothing left behind by the first one (stale partial sums, counters) leaks into
-the result.  The file sorts last so that a run stopping at the first failure has already run
+call checks that nothing left behind by the first one (accumulators, counters) leaks into the
+result.  The file sorts last so that a run stopping at the first failure has already run
 every other test.
 """
 import ctypes
@@ -57,7 +57,7 @@ def test_static_scratch_matches_caller_scratch_twice():
     for call in range(2):
         out = torch.full_like(expected, float("nan"))
         args = _args(q.packed(), plan, bq, bs, out)
-        status = lib.void_spmm_i8_static_scratch(ctypes.byref(args), plan.n_slots, plan.n_counters, _lib.stream_ptr())
+        status = lib.void_spmm_i8_static_scratch(ctypes.byref(args), plan.n_counters, _lib.stream_ptr())
         assert status == 0, lib.void_strerror(status)
         torch.cuda.synchronize()
         void.check_device_status()
@@ -74,9 +74,9 @@ def test_static_scratch_rejects_oversized_plans():
     plan = stream_k.stream_k_plan(q, 128, wl, n_cta=4)
     out = torch.empty(128, 128, device="cuda")
     args = _args(q.packed(), plan, bq.contiguous(), bs, out)
-    too_many_slots = (8 << 20) // (plan.np * 16384) + 1
-    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), too_many_slots, 1, _lib.stream_ptr()) == -8
-    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), 1, 4097, _lib.stream_ptr()) == -8
+    too_many_rows = (8 << 20) // (plan.np * 16384) + 1
+    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), too_many_rows, _lib.stream_ptr()) == -8
+    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), 4097, _lib.stream_ptr()) == -8
     assert b"maximum" in lib.void_strerror(-8)
     args.segs = None                                          # without a plan there is nothing to park
-    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), 0, 0, _lib.stream_ptr()) == -1
+    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), 0, _lib.stream_ptr()) == -1

@@ -154,8 +154,8 @@ def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chun
         if overflow:
             raise _lib.VoidB200Error("void_plan_segments: segment list overflow")
         partials = None
-        if n_slots:
-            partials = torch.empty(n_slots * np_ * PANEL * TILE, dtype=torch.int32, device=dev)
+        if n_ctr:   # one int32 accumulator per split row; the kernel leaves it zero again
+            partials = torch.zeros(n_ctr * np_ * PANEL * TILE, dtype=torch.int32, device=dev)
         counters = torch.zeros(max(n_ctr, 1), dtype=torch.int32, device=dev)
     return Plan(segs, cta_seg_ptr, n_cta, np_, n_chunks, n_segs, n_slots, n_ctr, partials, counters, mode,
                 chunk_tiles)

@@ -571,20 +571,23 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
             finish8<KIND>(od, s.row, n, m0, r, rs, cs, bias);
             if (epi_tid == 0 && q == 0) stamp(p, 10 + (c >> 3) * 2);
           } else {
-            // partial sum of a split row: park it (per thread 32 contiguous ints per panel)
-            uint4* dst = reinterpret_cast<uint4*>(p.partials) +
-                         (((size_t)(s.slot0 + s.my_idx) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8 + (m0 >> 2);
-            dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
-            dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+            // partial sum of a split row: added into the row's int32 accumulator in global memory
+            // (integer adds commute, so the total does not depend on which CTA comes first)
+            int32_t* dst = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
+                           (quad * 32 + lane);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
           }
         }
         cs = cs_next;
         bias = bias_next;
       }
       if (s.nseg > 1) {
-        // the CTA that arrives last adds the parked partial sums and finishes the row
+        // the CTA that arrives last reads the completed sums back and finishes the row
+        if (epi_tid == 0) stamp(p, 12);
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (epi_tid == 0) stamp(p, 13);
         if (epi_tid == 0) {
           const int old = atomicAdd(p.counters + s.ctr, 1);
           const int last = (old == s.nseg - 1) ? 1 : 0;
@@ -594,6 +597,8 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         const int last = last_s;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (epi_tid == 0) stamp(p, 14);
+        if (epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
         if (last) {
           __threadfence();
 #pragma unroll 1
@@ -607,20 +612,13 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
 #pragma unroll 1
             for (int c = 0; c < kColsPerWarp; c += 8) {
               const int m0 = m_first + c;
+              int32_t* src = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
+                             (quad * 32 + lane);
               uint32_t r[8];
 #pragma unroll
-              for (int k = 0; k < 8; ++k) r[k] = 0u;
-              for (int j = 0; j < s.nseg; ++j) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.partials) +
-                                   (((size_t)(s.slot0 + j) * p.np + q) * kPanelN + (quad * 32 + lane)) * 8 + (m0 >> 2);
-                const uint4 a = __ldcg(src), b = __ldcg(src + 1);
-                const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+              for (int k = 0; k < 8; ++k) r[k] = (uint32_t)__ldcg(src + k * kPanelN);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                  if (KIND == VOID_KIND_I8) r[k] += v[k];
-                  else r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(v[k]));
-                }
-              }
+              for (int k = 0; k < 8; ++k) src[k * kPanelN] = 0;  // left clean for the next launch
               finish8<KIND>(od, s.row, n, m0, r, rs, csq, biasq);
             }
           }
@@ -972,7 +970,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   int grid;
   if (a->segs != nullptr) {
     if (a->cta_seg_ptr == nullptr || a->n_cta <= 0 || a->panels_per_item == 0) return VOID_ERR_BAD_ARG;
-    if (drain) return VOID_ERR_BAD_ARG;  // split rows are finished by the row-accumulate kernel only
+    if (drain || kind != VOID_KIND_I8) return VOID_ERR_BAD_ARG;  // split rows: int32 row-accumulate kernel only
     grid = a->n_cta;
   } else {
     grid = a->grid > 0 ? a->grid : dev.sms * ctas_per_sm;
@@ -1043,10 +1041,10 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
 // ------------------------------------------------------------------------------------------
 // Built-in scratch for callers that cannot allocate device memory.
 // ------------------------------------------------------------------------------------------
-// Partial sums of split tile rows followed by their arrival counters.  The array lives in the
+// int32 accumulators of split tile rows followed by their arrival counters.  The array lives in the
 // library's device image: every GPU that loads the library holds these bytes until the process
 // exits.
-constexpr size_t kStaticPartialsBytes = 8u << 20;    // 8 MiB of int32 partial sums
+constexpr size_t kStaticPartialsBytes = 8u << 20;    // 8 MiB of int32 row accumulators
 constexpr int kStaticCounters = 4096;                // arrival counters (16 KiB)
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialsBytes + kStaticCounters * 4];
 
@@ -1068,11 +1066,11 @@ static int static_scratch_ptr(unsigned char** out) {
   return VOID_OK;
 }
 
-static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_slots, int32_t n_counters, cudaStream_t stream) {
-  if (a == nullptr || n_slots < 0 || n_counters < 0) return VOID_ERR_BAD_ARG;
+static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_split_rows, cudaStream_t stream) {
+  if (a == nullptr || n_split_rows < 0) return VOID_ERR_BAD_ARG;
   if (a->segs == nullptr || a->panels_per_item == 0) return VOID_ERR_BAD_ARG;  // a split-row plan is the point
-  const size_t slot_bytes = (size_t)a->panels_per_item * kPanelN * kTile * sizeof(int32_t);
-  if ((size_t)n_slots * slot_bytes > kStaticPartialsBytes || n_counters > kStaticCounters) return VOID_ERR_TOO_LARGE;
+  const size_t acc_bytes = (size_t)a->panels_per_item * kPanelN * kTile * sizeof(int32_t);  // one split row
+  if ((size_t)n_split_rows * acc_bytes > kStaticPartialsBytes || n_split_rows > kStaticCounters) return VOID_ERR_TOO_LARGE;
   unsigned char* base = nullptr;
   const int st = static_scratch_ptr(&base);
   if (st != VOID_OK) return st;
@@ -1080,12 +1078,14 @@ static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_slots, int3
   b.partials = base;
   b.partials_bytes = (int64_t)kStaticPartialsBytes;
   b.counters = reinterpret_cast<int32_t*>(base + kStaticPartialsBytes);
-  // The array keeps whatever the previous call left.  Partial sums are always written before they
-  // are read; the counters must start at zero (a launch that ran to the end leaves them so, a
-  // launch that gave up may not), so they are cleared in stream order before every launch.
-  if (n_counters > 0 &&
-      cudaMemsetAsync(b.counters, 0, (size_t)n_counters * sizeof(int32_t), stream) != cudaSuccess)
-    return VOID_ERR_CUDA;
+  // The array keeps whatever the previous call left.  Row accumulators and counters must start at
+  // zero (a launch that ran to the end leaves them so, a launch that gave up may not), so the part
+  // this call uses is cleared in stream order before the launch.
+  if (n_split_rows > 0) {
+    if (cudaMemsetAsync(b.partials, 0, (size_t)n_split_rows * acc_bytes, stream) != cudaSuccess) return VOID_ERR_CUDA;
+    if (cudaMemsetAsync(b.counters, 0, (size_t)n_split_rows * sizeof(int32_t), stream) != cudaSuccess)
+      return VOID_ERR_CUDA;
+  }
   return spmm_launch(&b, VOID_KIND_I8, stream);
 }
 
@@ -1093,9 +1093,8 @@ static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_slots, int3
 
 extern "C" {
 
-int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_slots, int32_t n_counters,
-                                void_stream_t stream) {
-  return vb::spmm_i8_static_scratch(args, n_slots, n_counters, reinterpret_cast<cudaStream_t>(stream));
+int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_split_rows, void_stream_t stream) {
+  return vb::spmm_i8_static_scratch(args, n_split_rows, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int void_spmm_i8(const void_spmm_args* args, void_stream_t stream) {
