@@ -606,21 +606,26 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
             const int n = n_base + q * kPanelN;
             float csq = p.b_scale, biasq = 0.0f;
             if (n < p.N) {
-              if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
-              if (p.bias != nullptr) biasq = __ldg(p.bias + n);
+              if (p.col_scale != nullptr) csq = __ldcg(p.col_scale + n) * p.b_scale;
+              if (p.bias != nullptr) biasq = __ldcg(p.bias + n);
             }
-#pragma unroll 1
-            for (int c = 0; c < kColsPerWarp; c += 8) {
-              const int m0 = m_first + c;
-              int32_t* src = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
-                             (quad * 32 + lane);
-              uint32_t r[8];
+            // all of this warp's sums of the panel are requested at once (one L2 round trip), then
+            // the accumulator is cleared for the next launch
+            int32_t* src = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
+                           (quad * 32 + lane);
+            uint32_t r[kColsPerWarp];
 #pragma unroll
-              for (int k = 0; k < 8; ++k) r[k] = (uint32_t)__ldcg(src + k * kPanelN);
+            for (int k = 0; k < kColsPerWarp; ++k) r[k] = (uint32_t)__ldcg(src + k * kPanelN);
 #pragma unroll
-              for (int k = 0; k < 8; ++k) src[k * kPanelN] = 0;  // left clean for the next launch
-              finish8<KIND>(od, s.row, n, m0, r, rs, csq, biasq);
+            for (int k = 0; k < kColsPerWarp; ++k) src[k * kPanelN] = 0;
+            if (od.acc_out != nullptr && n < od.N) {
+              uint32_t* a = reinterpret_cast<uint32_t*>(od.acc_out) + ((size_t)s.row * kTile + m_first) * od.N + n;
+#pragma unroll
+              for (int k = 0; k < kColsPerWarp; ++k) a[(size_t)k * od.N] = r[k];
             }
+            OutDesc od2 = od;
+            od2.acc_out = nullptr;
+            finish_cols<KIND>(od2, s.row, n, m_first, r, rs, csq, biasq);
           }
         }
       }
