@@ -904,8 +904,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   int np = a->panels_per_item;
   if (np != 0 && np != 1 && np != 2 && np != 4) return VOID_ERR_BAD_ARG;
   if (np == 0) {
-    np = total_panels >= 4 ? 4 : (total_panels >= 2 ? 2 : 1);
-    if (drain && np > 2) np = 2;
+    // two panels per item keep two CTAs on an SM, which measured faster than four panels with one
+    np = total_panels >= 2 ? 2 : 1;
     if (a->segs == nullptr) {  // keep enough work items to fill the machine
       while (np > 1 && (long long)a->nbr * ((total_panels + np - 1) / np) < 2ll * dev.sms) np >>= 1;
     }

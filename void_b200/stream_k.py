@@ -49,7 +49,7 @@ def compute_stream_k_workload(void_tensor, n_workers: Optional[int] = None,
 
 def _plan_for(a: Int8VOIDTensor, packed, N: int, workload: StreamKWorkload, per_worker: bool, n_cta: Optional[int]):
     panels = (N + 127) // 128
-    np_ = 4 if panels >= 4 else (2 if panels >= 2 else 1)
+    np_ = 2 if panels >= 2 else 1
     if n_cta is None:
         n_cta = _spmm.sm_count(packed.tiles.device) * (1 if np_ == 4 else 2)
     mode = 2 if per_worker else 1
