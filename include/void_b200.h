@@ -219,6 +219,8 @@ typedef struct void_spmm_args {
   int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1, 2, 4 or 8      */
   /* debugging aid: when not NULL, 64 uint64 nanosecond timestamps per launched CTA      */
   void* trace;
+  int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM) */
+  int32_t reserved;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

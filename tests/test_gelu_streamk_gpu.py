@@ -114,11 +114,13 @@ def test_stream_k_worker_partials_bit_exact():
     b_np = bq.cpu().numpy()
     ref_acc = vo.spmm_int8_acc(*args, b_np)
     assert np.array_equal(acc.cpu().numpy(), ref_acc)
-    # one segment per worker of the table (n_chunks = 1 here; N = 192 is one chunk of two panels)
-    worker_segs = segs[segs[:, 3] > segs[:, 2]]
-    assert np.array_equal(worker_segs[:, 0], wl.worker_rows.cpu().numpy())
-    assert np.array_equal(worker_segs[:, 2], wl.worker_block_start.cpu().numpy())
-    assert np.array_equal(worker_segs[:, 3], wl.worker_block_end.cpu().numpy())
+    # one segment per worker of the table and per column chunk of the plan
+    chunk_cols = plan.np * 128
+    for ch in range(plan.n_chunks):
+        worker_segs = segs[(segs[:, 3] > segs[:, 2]) & (segs[:, 1] == ch)]
+        assert np.array_equal(worker_segs[:, 0], wl.worker_rows.cpu().numpy())
+        assert np.array_equal(worker_segs[:, 2], wl.worker_block_start.cpu().numpy())
+        assert np.array_equal(worker_segs[:, 3], wl.worker_block_end.cpu().numpy())
     parts_np = parts.cpu().numpy()
     total = np.zeros_like(ref_acc)
     rng = np.random.default_rng(0)
@@ -126,8 +128,10 @@ def test_stream_k_worker_partials_bit_exact():
     for i, (row, ch, t0, t1, nseg, slot0, idx, ctr) in enumerate(segs):
         total[row * 32:(row + 1) * 32] += parts_np[i]
         if i in check:
+            cols = slice(ch * chunk_cols, min((ch + 1) * chunk_cols, 192))
             ref_part = vo.spmm_int8_acc(*args, b_np, t_range=(int(t0), int(t1)))[row * 32:(row + 1) * 32]
-            assert np.array_equal(parts_np[i], ref_part)
+            assert np.array_equal(parts_np[i][:, cols], ref_part[:, cols])
+            assert not np.delete(parts_np[i], np.arange(cols.start, cols.stop), axis=1).any()
     assert np.array_equal(total, ref_acc)                     # sum of partials = row accumulator
     plain = void.void_spmm_int8(q, bq, bs)
     assert torch.equal(c, plain)

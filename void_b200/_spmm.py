@@ -101,6 +101,16 @@ class Plan:
     chunk_tiles: int
 
 
+def default_panels(nbr: int, N: int, sms: int) -> int:
+    """Panels per work item the library picks by itself (same rule as the C launcher): two, unless
+    that leaves fewer work items than four per SM."""
+    panels = (N + PANEL - 1) // PANEL
+    np_ = 2 if panels >= 2 else 1
+    while np_ > 1 and nbr * ((panels + np_ - 1) // np_) < 4 * sms:
+        np_ //= 2
+    return np_
+
+
 def sm_count(device) -> int:
     with torch.cuda.device(device):
         return _lib.load().void_device_sm_count()
@@ -177,7 +187,7 @@ def prepare_b(b: torch.Tensor) -> torch.Tensor:
 def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode: int, col_scale=None,
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
-         grid: int = 0, tiles_per_stage: int = 0, trace=None) -> torch.Tensor:
+         grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None) -> torch.Tensor:
     """One launch of void_spmm_i8 / void_spmm_f8 on the current stream of b's device."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
@@ -224,6 +234,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     a.status = _lib.status_word(dev).data_ptr()
     a.panels_per_item, a.stages, a.grid, a.tiles_per_stage = panels_per_item, stages, grid, tiles_per_stage
     a.trace = None if trace is None else trace.data_ptr()
+    a.cta_shape = cta_shape
     fn = lib.void_spmm_i8 if packed.kind == _lib.KIND_I8 else lib.void_spmm_f8
     with torch.cuda.device(dev):
         _lib.check(fn(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm")

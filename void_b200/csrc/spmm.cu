@@ -50,13 +50,24 @@ constexpr int kPanelN = 128;
 constexpr int kPanelBytes = kTile * kPanelN;  // 4096
 constexpr int kMaxStages = 16;
 constexpr int kMaxSlots = 16;
-constexpr int kProducerWarps = 4;   // warps 0..3 stream tiles and panels
-constexpr int kMmaWarp = kProducerWarps;  // warp 4 issues the MMAs (and owns the TMEM allocation)
-constexpr int kFirstEpiWarp = kMmaWarp + 1;
-constexpr int kEpiWarps = 8;        // warps 5..12: two per TMEM lane quadrant
-constexpr int kEpiThreads = 32 * kEpiWarps;
-constexpr int kThreads = 32 * kFirstEpiWarp + kEpiThreads;
-constexpr int kColsPerWarp = 32 / (kEpiWarps / 4);  // accumulator columns one epilogue warp reads
+// Warp roles of a CTA: PW producer warps (0..PW-1) stream tiles and panels, warp PW issues the MMAs
+// and owns the TMEM allocation, EW epilogue warps follow (EW/4 per TMEM lane quadrant, each taking
+// 32/(EW/4) accumulator columns).  Two shapes are built: a wide one (4 + 1 + 8 warps, two CTAs per
+// SM) and a slim one (2 + 1 + 4 warps, four CTAs per SM).  The pipeline is latency-bound on the
+// single MMA-issuing thread of a CTA, so four slim CTAs per SM move more tiles than two wide ones.
+template <int PW_, int EW_, int CTAS_>
+struct Shape {
+  static constexpr int PW = PW_;
+  static constexpr int EW = EW_;
+  static constexpr int MMA = PW_;
+  static constexpr int EPI0 = PW_ + 1;
+  static constexpr int EPI_THREADS = 32 * EW_;
+  static constexpr int THREADS = 32 * (PW_ + 1 + EW_);
+  static constexpr int COLS = 32 / (EW_ / 4);  // accumulator columns one epilogue warp reads
+  static constexpr int CTAS_PER_SM = CTAS_;
+};
+using Wide = Shape<4, 8, 2>;
+using Slim = Shape<2, 4, 4>;
 
 // device status codes (written to the status word)
 constexpr int kStatusTimeout = 1;
@@ -216,22 +227,21 @@ __device__ __forceinline__ void finish8(const OutDesc& o, int row, int n, int m0
   store8(o, row, n, m0, v);
 }
 
-// Fast epilogue of one warp's share of a panel: kColsPerWarp raw accumulators of output column n
-// straight to C (no raw-accumulator dump, no split row), stores specialised per output type.
+// Fast epilogue of sixteen raw accumulators of output column n (tile rows m0 .. m0 + 15) straight to C
+// (no raw-accumulator dump, no split row), stores specialised per output type.
 template <int KIND>
-__device__ __forceinline__ void finish_cols(const OutDesc& o, int row, int n, int m0,
-                                            const uint32_t (&r)[kColsPerWarp], float row_scale, float cs,
-                                            float bias) {
+__device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+                                         float row_scale, float cs, float bias) {
   if (n >= o.N) return;
-  float v[kColsPerWarp];
+  float v[16];
 #pragma unroll
-  for (int k = 0; k < kColsPerWarp; ++k) {
+  for (int k = 0; k < 16; ++k) {
     const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
     v[k] = (x * row_scale) * cs + bias;
   }
   if (o.act != VOID_ACT_NONE) {
 #pragma unroll
-    for (int k = 0; k < kColsPerWarp; ++k) {
+    for (int k = 0; k < 16; ++k) {
       if (o.act == VOID_ACT_GELU) v[k] = gelu_tanh_sigmoid(v[k]);
       else if (o.act == VOID_ACT_RELU) v[k] = fmaxf(v[k], 0.0f);
       else v[k] = v[k] * fast_sigmoid(v[k]);
@@ -243,17 +253,17 @@ __device__ __forceinline__ void finish_cols(const OutDesc& o, int row, int n, in
   if (o.dtype == VOID_OUT_F16) {
     __half* dst = reinterpret_cast<__half*>(o.out) + first;
 #pragma unroll
-    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+    for (int k = 0; k < 16; ++k, dst += o.ldc)
       if (k < rows) *dst = __float2half_rn(v[k]);
   } else if (o.dtype == VOID_OUT_BF16) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(o.out) + first;
 #pragma unroll
-    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+    for (int k = 0; k < 16; ++k, dst += o.ldc)
       if (k < rows) *dst = __float2bfloat16_rn(v[k]);
   } else {
     float* dst = reinterpret_cast<float*>(o.out) + first;
 #pragma unroll
-    for (int k = 0; k < kColsPerWarp; ++k, dst += o.ldc)
+    for (int k = 0; k < 16; ++k, dst += o.ldc)
       if (k < rows) *dst = v[k];
   }
 }
@@ -273,8 +283,9 @@ __device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
   return (uint32_t)(p.group * p.np) * kPanelBytes + (uint32_t)j * kTileBytes;
 }
 
-// Producer warp `pw` of kProducerWarps: the CTA's groups of tiles are numbered in the order the
-// MMA warp consumes them; group g uses ring stage g % stages and belongs to warp g % kProducerWarps.
+// Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
+// consumes them; group g uses ring stage g % stages and belongs to warp g % C::PW.
+template <class C>
 __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtensorMap* tmap, PipeBars* bars,
                                               uint32_t ring_base, uint32_t stage_bytes, volatile int* abort_flag,
                                               int lane, int pw) {
@@ -291,18 +302,18 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     const int n0 = s.chunk * p.np * kPanelN;
     const uint32_t unit_bytes = (uint32_t)(kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes);
     const int ngroups = (s.t1 - s.t0 + G - 1) / G;
-    int k = pw - g % kProducerWarps;
-    if (k < 0) k += kProducerWarps;
+    int k = pw - g % C::PW;
+    if (k < 0) k += C::PW;
     // block column of this lane's tile in the warp's next group, fetched one group ahead
     int col = 0;
     if (k < ngroups && lane < G && s.t0 + k * G + lane < s.t1) col = __ldg(p.tile_cols + s.t0 + k * G + lane);
-    for (; k < ngroups; k += kProducerWarps) {
+    for (; k < ngroups; k += C::PW) {
       const int gi = g + k;
       const int stage = gi % p.stages;
       const uint32_t phase = (uint32_t)(gi / p.stages) & 1u;
       const int t = s.t0 + k * G;
       const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-      const int kn = k + kProducerWarps;
+      const int kn = k + C::PW;
       int col_next = 0;
       if (kn < ngroups && lane < G && s.t0 + kn * G + lane < s.t1) col_next = __ldg(p.tile_cols + s.t0 + kn * G + lane);
       const uint32_t full = smem_u32(&bars->full[stage]);
@@ -338,6 +349,7 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, ui
   else mma_f8(d, a, b, idesc, acc);
 }
 
+template <class C>
 __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtensorMap* tmap, PipeBars& bars,
                                                uint32_t* tmem_base_s, int* abort_s, int n_acc, uint32_t tmem_cols) {
   const int warp = threadIdx.x >> 5;
@@ -349,12 +361,12 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
     }
     for (int b = 0; b < n_acc; ++b) {
       mbar_init(smem_u32(&bars.acc_full[b]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[b]), kEpiWarps);
+      mbar_init(smem_u32(&bars.acc_empty[b]), C::EW);
     }
     fence_mbar_init();
     if (p.tiles != nullptr) prefetch_tmap(tmap);
   }
-  if (warp == kMmaWarp) {
+  if (warp == C::MMA) {
     tmem_alloc(smem_u32(tmem_base_s), tmem_cols);
     tmem_relinquish();
   }
@@ -370,6 +382,7 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
   if (threadIdx.x == 0) stamp(p, 1);
 }
 
+template <class C>
 __device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abort_s, uint32_t tmem_base,
                                                   uint32_t tmem_cols) {
   tc_fence_before();
@@ -384,14 +397,14 @@ __device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abor
     if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusTimeout);
     __syncthreads();
   }
-  if ((threadIdx.x >> 5) == kMmaWarp) tmem_dealloc(tmem_base, tmem_cols);
+  if ((threadIdx.x >> 5) == C::MMA) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // ------------------------------------------------------------------------------------------
 // Row-accumulate kernel.
 // ------------------------------------------------------------------------------------------
-template <int KIND>
-__global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
+template <int KIND, class C>
+__global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
                                                                const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
@@ -410,13 +423,13 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
   volatile int* abort_flag = &abort_s;
 
   if (threadIdx.x == 0) last_s = 0;
-  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
+  pipeline_setup<C>(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp < kProducerWarps) {
-    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+  if (warp < C::PW) {
+    producer_loop<C>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
     if (warp == 0 && lane == 0) stamp(p, 2);
-  } else if (warp == kMmaWarp) {
+  } else if (warp == C::MMA) {
     if (lane == 0) {
       // Everything an MMA needs is kept in registers and advanced by constants: this thread runs
       // alone on its scheduler, so every dependent instruction between two MMAs costs its full
@@ -483,10 +496,10 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
     // epilogue warps: TMEM lane quadrant = warp id mod 4; the two warps of a quadrant split the
     // 32 accumulator columns (tile rows m) in halves
     const int quad = warp & 3;
-    const int half = (warp - kFirstEpiWarp) >> 2;
-    const int epi_tid = (int)threadIdx.x - 32 * kFirstEpiWarp;
+    const int half = (warp - C::EPI0) >> 2;
+    const int epi_tid = (int)threadIdx.x - 32 * C::EPI0;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-    const int m_first = half * kColsPerWarp;
+    const int m_first = half * C::COLS;
     const OutDesc od = out_desc(p);
     int begin, end, step;
     seg_range(p, begin, end, step);
@@ -510,7 +523,7 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
       // one thread waits, the named barrier hands its verdict to all epilogue warps, so that they
       // leave the loop together if the wait gave up
       if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, abort_flag) ? 1 : 0;
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
       if (!ok_s[it & 1u]) break;
       if (epi_tid == 0 && i == begin) stamp(p, 5);
       if (epi_tid == 0) stamp(p, 8);
@@ -525,28 +538,29 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
           if (p.bias != nullptr) bias_next = __ldg(p.bias + n + kPanelN);
         }
         if (fast) {
-          uint32_t r[kColsPerWarp];
-          if (has) {
-            const uint32_t taddr = tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first);
-            if (kColsPerWarp == 16) tmem_ld_32x16(taddr, reinterpret_cast<uint32_t(&)[16]>(r));
-            else tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(r));
-            tmem_ld_wait();
-          } else {
 #pragma unroll
-            for (int k = 0; k < kColsPerWarp; ++k) r[k] = 0u;
+          for (int c = 0; c < C::COLS; c += 16) {
+            uint32_t r[16];
+            if (has) {
+              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) r[k] = 0u;
+            }
+            if (q == npan - 1 && c + 16 >= C::COLS) {  // this warp is done with the accumulator buffer
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+            }
+            finish16<KIND>(od, s.row, n, m_first + c, r, rs, cs, bias);
           }
-          if (q == npan - 1) {  // this warp is done with the accumulator buffer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-          }
-          finish_cols<KIND>(od, s.row, n, m_first, r, rs, cs, bias);
           cs = cs_next;
           bias = bias_next;
           continue;
         }
 #pragma unroll 1
-        for (int c = 0; c < kColsPerWarp; c += 8) {
+        for (int c = 0; c < C::COLS; c += 8) {
           const int m0 = m_first + c;
           uint32_t r[8];
           if (has) {
@@ -557,7 +571,7 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
             for (int k = 0; k < 8; ++k) r[k] = 0u;
           }
           if (epi_tid == 0 && q == 0) stamp(p, 9 + (c >> 3) * 2);
-          if (q == npan - 1 && c + 8 >= kColsPerWarp) {  // this warp is done with the accumulator buffer
+          if (q == npan - 1 && c + 8 >= C::COLS) {  // this warp is done with the accumulator buffer
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
@@ -586,7 +600,7 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
         // the CTA that arrives last reads the completed sums back and finishes the row
         if (epi_tid == 0) stamp(p, 12);
         __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         if (epi_tid == 0) stamp(p, 13);
         if (epi_tid == 0) {
           const int old = atomicAdd(p.counters + s.ctr, 1);
@@ -594,9 +608,9 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
           if (last) p.counters[s.ctr] = 0;  // left clean for the next launch
           last_s = last;
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         const int last = last_s;
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         if (epi_tid == 0) stamp(p, 14);
         if (epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
         if (last) {
@@ -613,33 +627,36 @@ __global__ void __launch_bounds__(kThreads) spmm_rowacc_kernel(const __grid_cons
             // the accumulator is cleared for the next launch
             int32_t* src = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
                            (quad * 32 + lane);
-            uint32_t r[kColsPerWarp];
 #pragma unroll
-            for (int k = 0; k < kColsPerWarp; ++k) r[k] = (uint32_t)__ldcg(src + k * kPanelN);
+            for (int c = 0; c < C::COLS; c += 16) {
+              uint32_t r[16];
 #pragma unroll
-            for (int k = 0; k < kColsPerWarp; ++k) src[k * kPanelN] = 0;
-            if (od.acc_out != nullptr && n < od.N) {
-              uint32_t* a = reinterpret_cast<uint32_t*>(od.acc_out) + ((size_t)s.row * kTile + m_first) * od.N + n;
+              for (int k = 0; k < 16; ++k) r[k] = (uint32_t)__ldcg(src + (c + k) * kPanelN);
 #pragma unroll
-              for (int k = 0; k < kColsPerWarp; ++k) a[(size_t)k * od.N] = r[k];
+              for (int k = 0; k < 16; ++k) src[(c + k) * kPanelN] = 0;
+              if (od.acc_out != nullptr && n < od.N) {
+                uint32_t* a = reinterpret_cast<uint32_t*>(od.acc_out) + ((size_t)s.row * kTile + m_first + c) * od.N + n;
+#pragma unroll
+                for (int k = 0; k < 16; ++k) a[(size_t)k * od.N] = r[k];
+              }
+              OutDesc od2 = od;
+              od2.acc_out = nullptr;
+              finish16<KIND>(od2, s.row, n, m_first + c, r, rs, csq, biasq);
             }
-            OutDesc od2 = od;
-            od2.acc_out = nullptr;
-            finish_cols<KIND>(od2, s.row, n, m_first, r, rs, csq, biasq);
           }
         }
       }
     }
     if (epi_tid == 0) stamp(p, 6);
   }
-  pipeline_teardown(p, &abort_s, tmem_base, tmem_cols);
+  pipeline_teardown<C>(p, &abort_s, tmem_base, tmem_cols);
 }
 
 // ------------------------------------------------------------------------------------------
 // Per-tile drain kernel: every tile's product is scaled by that tile's scale.
 // ------------------------------------------------------------------------------------------
-template <int KIND, int NP>
-__global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_constant__ CUtensorMap tmap_b,
+template <int KIND, int NP, class C>
+__global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) spmm_drain_kernel(const __grid_constant__ CUtensorMap tmap_b,
                                                               const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
@@ -651,7 +668,7 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
   // stage, not once per tile.
   constexpr uint32_t kTileCols = NP * 32;   // TMEM columns of one tile's product
   const uint32_t kTmemCols = (uint32_t)p.tmem_cols;
-  constexpr int CW = kColsPerWarp;
+  constexpr int CW = C::COLS;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -661,13 +678,13 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
   const int n_slots = (int)(kTmemCols / group_cols);   // >= 2: checked at launch
   volatile int* abort_flag = &abort_s;
 
-  pipeline_setup(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
+  pipeline_setup<C>(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp < kProducerWarps) {
-    producer_loop(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+  if (warp < C::PW) {
+    producer_loop<C>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
     if (warp == 0 && lane == 0) stamp(p, 2);
-  } else if (warp == kMmaWarp) {
+  } else if (warp == C::MMA) {
     if (lane == 0) {
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
@@ -720,7 +737,7 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
     __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - kFirstEpiWarp) >> 2;
+    const int half = (warp - C::EPI0) >> 2;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
     const int m_first = half * CW;
     const OutDesc od = out_desc(p);
@@ -757,19 +774,21 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
 #pragma unroll
           for (int q = 0; q < NP; ++q) {
             if (q < npan) {
-              uint32_t r[CW];
-              if (CW == 16) tmem_ld_32x16(tile_addr + (uint32_t)q * 32u, reinterpret_cast<uint32_t(&)[16]>(r));
-              else tmem_ld_32x32(tile_addr + (uint32_t)q * 32u, reinterpret_cast<uint32_t(&)[32]>(r));
-              tmem_ld_wait();
-              if (j == gcnt - 1 && q == npan - 1) {  // this warp has read the whole slot group
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
-              }
 #pragma unroll
-              for (int m = 0; m < CW; ++m) {
-                const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
-                acc[q][m] = fmaf(ts, x, acc[q][m]);
+              for (int c = 0; c < CW; c += 16) {
+                uint32_t r[16];
+                tmem_ld_32x16(tile_addr + (uint32_t)(q * 32 + c), r);
+                tmem_ld_wait();
+                if (j == gcnt - 1 && q == npan - 1 && c + 16 >= CW) {  // this warp has read the whole slot group
+                  tc_fence_before();
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
+                }
+#pragma unroll
+                for (int m = 0; m < 16; ++m) {
+                  const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
+                  acc[q][c + m] = fmaf(ts, x, acc[q][c + m]);
+                }
               }
             }
           }
@@ -801,9 +820,9 @@ __global__ void __launch_bounds__(kThreads) spmm_drain_kernel(const __grid_const
         }
       }
     }
-    if (threadIdx.x == 32 * kFirstEpiWarp) stamp(p, 6);
+    if (threadIdx.x == 32 * C::EPI0) stamp(p, 6);
   }
-  pipeline_teardown(p, &abort_s, tmem_base, kTmemCols);
+  pipeline_teardown<C>(p, &abort_s, tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -865,11 +884,11 @@ static int ensure_smem(const void* kernel, int bytes) {
 }
 
 template <typename Kernel>
-static void launch_pdl(Kernel kernel, int grid, int smem_bytes, cudaStream_t stream, const CUtensorMap& tmap,
-                       const SpmmParams& p) {
+static void launch_pdl(Kernel kernel, int grid, int threads, int smem_bytes, cudaStream_t stream,
+                       const CUtensorMap& tmap, const SpmmParams& p) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3((unsigned)threads);
   cfg.dynamicSmemBytes = (size_t)smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -907,27 +926,37 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     // two panels per item keep two CTAs on an SM, which measured faster than four panels with one
     np = total_panels >= 2 ? 2 : 1;
     if (a->segs == nullptr) {  // keep enough work items to fill the machine
-      while (np > 1 && (long long)a->nbr * ((total_panels + np - 1) / np) < 2ll * dev.sms) np >>= 1;
+      while (np > 1 && (long long)a->nbr * ((total_panels + np - 1) / np) < 4ll * dev.sms) np >>= 1;
     }
   }
   const int n_chunks = (total_panels + np - 1) / np;
-  const int ctas_per_sm = (np == 4) ? 1 : 2;
+  // CTA shape: the slim one (four CTAs per SM) for the row-accumulate kernel with at most two panels
+  // per item; the wide one for the per-tile kernel and for four-panel items (TMEM: 2 x np x 32
+  // columns per row-accumulate CTA, 512 per SM)
+  int shape = a->cta_shape;
+  if (shape < 0 || shape > 2) return VOID_ERR_BAD_ARG;
+  if (shape == 0) shape = ((!drain && np <= 2) || (drain && np == 1)) ? 2 : 1;
+  if (shape == 2 && (np > 2 || (drain && np > 1))) return VOID_ERR_BAD_ARG;
+  const bool slim = (shape == 2);
+  const int producer_warps = slim ? Slim::PW : Wide::PW;
+  const int ctas_per_sm = slim ? Slim::CTAS_PER_SM : ((np == 4) ? 1 : Wide::CTAS_PER_SM);
   int group = a->tiles_per_stage;  // 0 = default
-  if (group == 0) group = (np == 1) ? 4 : 2;
+  if (group == 0) group = (np == 1) ? 4 : 2;  // few, large ring stages beat a deep ring of small ones
   if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
+  if (drain && slim && a->tiles_per_stage == 0) group = 2;
   const int drain_tmem = 512 / ctas_per_sm;
   if (drain && group * np * 32 * 2 > drain_tmem) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
   const int stage_bytes = group * (np * kPanelBytes + kTileBytes);
   int stages = a->stages;
   if (stages == 0) {
-    const int budget = (200 * 1024) / ctas_per_sm;
+    const int budget = (216 * 1024) / ctas_per_sm - 2048;
     stages = budget / stage_bytes;
     if (stages > 8) stages = 8;
   }
-  // A producer warp may run up to kProducerWarps - 1 groups ahead of the consumer's order; the
+  // A producer warp may run up to (producer warps - 1) groups ahead of the consumer's order; the
   // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
   // hold at least one stage per producer warp.
-  if (stages < kProducerWarps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
+  if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
   const int smem_bytes = stages * stage_bytes + 1024;
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
@@ -1014,32 +1043,31 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (r != CUDA_SUCCESS) return VOID_ERR_TENSOR_MAP;
   }
 
-  const int max_ring = smem_bytes;
+#define VB_LAUNCH(KERNEL, SHAPE)                                                               \
+  do {                                                                                        \
+    if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
+    launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, p);                    \
+  } while (0)
   if (!drain) {
     if (kind == VOID_KIND_I8) {
-      if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_I8>, max_ring)) return VOID_ERR_CUDA;
-      launch_pdl(spmm_rowacc_kernel<VOID_KIND_I8>, grid, smem_bytes, stream, tmap, p);
+      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
+      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Wide>), Wide);
     } else {
-      if (ensure_smem((const void*)spmm_rowacc_kernel<VOID_KIND_F8E4M3>, max_ring)) return VOID_ERR_CUDA;
-      launch_pdl(spmm_rowacc_kernel<VOID_KIND_F8E4M3>, grid, smem_bytes, stream, tmap, p);
+      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Slim>), Slim);
+      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Wide>), Wide);
     }
+  } else if (kind == VOID_KIND_I8) {
+    if (np == 1 && slim) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim>), Slim);
+    else if (np == 1) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Wide>), Wide);
+    else if (np == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 2, Wide>), Wide);
+    else VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 4, Wide>), Wide);
   } else {
-#define VB_LAUNCH_DRAIN(KIND, NP)                                                      \
-  do {                                                                                 \
-    if (ensure_smem((const void*)spmm_drain_kernel<KIND, NP>, max_ring)) return VOID_ERR_CUDA; \
-    launch_pdl(spmm_drain_kernel<KIND, NP>, grid, smem_bytes, stream, tmap, p);                \
-  } while (0)
-    if (kind == VOID_KIND_I8) {
-      if (np == 1) VB_LAUNCH_DRAIN(VOID_KIND_I8, 1);
-      else if (np == 2) VB_LAUNCH_DRAIN(VOID_KIND_I8, 2);
-      else VB_LAUNCH_DRAIN(VOID_KIND_I8, 4);
-    } else {
-      if (np == 1) VB_LAUNCH_DRAIN(VOID_KIND_F8E4M3, 1);
-      else if (np == 2) VB_LAUNCH_DRAIN(VOID_KIND_F8E4M3, 2);
-      else VB_LAUNCH_DRAIN(VOID_KIND_F8E4M3, 4);
-    }
-#undef VB_LAUNCH_DRAIN
+    if (np == 1 && slim) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim>), Slim);
+    else if (np == 1) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Wide>), Wide);
+    else if (np == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 2, Wide>), Wide);
+    else VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 4, Wide>), Wide);
   }
+#undef VB_LAUNCH
   return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
 }
 

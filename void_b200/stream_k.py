@@ -48,10 +48,10 @@ def compute_stream_k_workload(void_tensor, n_workers: Optional[int] = None,
 
 
 def _plan_for(a: Int8VOIDTensor, packed, N: int, workload: StreamKWorkload, per_worker: bool, n_cta: Optional[int]):
-    panels = (N + 127) // 128
-    np_ = 2 if panels >= 2 else 1
+    sms = _spmm.sm_count(packed.tiles.device)
+    np_ = _spmm.default_panels(packed.nbr, N, sms)
     if n_cta is None:
-        n_cta = _spmm.sm_count(packed.tiles.device) * (1 if np_ == 4 else 2)
+        n_cta = sms * 4          # four slim CTAs per SM
     mode = 2 if per_worker else 1
     key = ("streamk", N, np_, n_cta, mode, workload.chunk_tiles)
     cache = getattr(a, "_plan_cache", None)
