@@ -45,8 +45,10 @@ enum {
   VOID_ERR_TENSOR_MAP = -9      /* the driver refused the copy-engine descriptor of B    */
 };
 
-/* element kinds of the 8-bit operands */
-enum { VOID_KIND_I8 = 0, VOID_KIND_F8E4M3 = 1 };
+/* element kinds of the operands: 8-bit quantised (void_spmm_i8 / void_spmm_f8) and floating
+ * point (void_spmm_fp; fp32 operands are multiplied as TF32, the precision tl.dot uses for
+ * the reference's fp32 kernel on a GPU) */
+enum { VOID_KIND_I8 = 0, VOID_KIND_F8E4M3 = 1, VOID_KIND_F16 = 2, VOID_KIND_BF16 = 3, VOID_KIND_TF32 = 4 };
 /* output element types */
 enum { VOID_OUT_F32 = 0, VOID_OUT_F16 = 1, VOID_OUT_BF16 = 2 };
 /* epilogue activation codes; same numbering as get_activation_code, void/fusion.py:77-91 */
@@ -92,6 +94,15 @@ VOID_API int void_pack_tiles(const void* values, const float* scales, int64_t n_
                     const int32_t* row_ptr, int64_t nnz, int32_t nbr, void* packed,
                     int32_t* tile_cols, float* tile_scales, float* row_scale,
                     void_stream_t stream);
+
+/* Same gather for floating-point tiles (VOIDTensor.values, void/format.py:66): elem_bytes = 2
+ * (fp16 / bf16) or 4 (fp32).  A packed tile takes 1024 * elem_bytes bytes and is stored as
+ * [row / 8][k-chunk][row % 8][16 bytes] with 2 * elem_bytes 16-byte k-chunks per row, the order
+ * the tensor cores read a K-major operand in.  fp32 tiles are rounded to the nearest TF32 value
+ * on the way (the tensor cores would otherwise truncate them).  packed must be 1024-byte aligned. */
+VOID_API int void_pack_tiles_fp(const void* values, int32_t elem_bytes, const int32_t* block_cols,
+                                const int32_t* block_indices, int64_t nnz, void* packed,
+                                int32_t* tile_cols, void_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Quantisers.
@@ -178,14 +189,14 @@ VOID_API int void_plan_segments_host(const int32_t* row_ptr, int32_t nbr, int32_
  * ------------------------------------------------------------------------------------- */
 typedef struct void_spmm_args {
   /* A, packed (see void_pack_tiles) */
-  const void* tiles;        /* nnz * 1024 bytes, 1024-byte aligned                       */
+  const void* tiles;        /* nnz * 1024 * element bytes, 1024-byte aligned             */
   const int32_t* tile_cols; /* [nnz] block column of each packed tile                    */
   const float* tile_scales; /* [nnz] tile scales in packed order (VOID_SCALE_PER_TILE)   */
   const int32_t* row_ptr;   /* [nbr+1]                                                   */
   const float* row_scale;   /* [nbr] mean tile scale per row (VOID_SCALE_ROW_MEAN)       */
   int32_t nbr, nbc;
   int64_t nnz;
-  /* B, row-major [K, N] 8-bit, ldb bytes between k rows (multiple of 16)                */
+  /* B, row-major [K, N], ldb BYTES between k rows (multiple of 16)                       */
   const void* b;
   int64_t ldb;
   int32_t K, N;
@@ -225,6 +236,21 @@ typedef struct void_spmm_args {
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);
 VOID_API int void_spmm_f8(const void_spmm_args* args, void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Floating-point product.  Replaces void_spmm_kernel / void_spmm, void/ops.py:43-217; with
+ * act / bias also void_spmm_activation_kernel / void_spmm_gelu on a floating VOIDTensor,
+ * void/fusion.py:98-198, :381-399; with a plan also stream_k_spmm_kernel / void_spmm_stream_k,
+ * void/stream_k.py:113-301.
+ * kind = VOID_KIND_TF32 (A tiles and B are fp32; products in TF32, fp32 accumulation),
+ * VOID_KIND_F16 or VOID_KIND_BF16 (A tiles and B in that type; exact products, fp32
+ * accumulation).  args->tiles comes from void_pack_tiles_fp; args->ldb is in BYTES and a
+ * multiple of 16; scale_mode must be VOID_SCALE_ROW_MEAN with row_scale == NULL (no scales);
+ * col_scale / b_scale / bias / act / out_dtype work as in void_spmm_i8.  With a plan, the
+ * pieces of a split row are added with fp32 atomic adds, so the last bits of such rows can
+ * differ from run to run (the reference's spin-lock version has the same property).
+ * ------------------------------------------------------------------------------------- */
+VOID_API int void_spmm_fp(const void_spmm_args* args, int32_t kind, void_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * void_spmm_i8 for callers that have no way to hand over scratch memory.  (This entry point has

@@ -147,6 +147,29 @@ def _b_block(b, c, K):
     return blk
 
 
+def spmm_fp(values, block_rows, block_cols, shape, b, t_range=None):
+    """fp32 result of void_spmm_kernel, void/ops.py:93-146: for every tile of the row, in row order,
+    acc += float32(A tile) @ float32(B block) with an fp32 accumulator (on a GPU tl.dot rounds the
+    operands to TF32, so a device result agrees to about 1e-3, the bar of tests/test_all_features.py:48).
+    With t_range=(t0, t1) only the tiles at row-ordered positions [t0, t1) are added (one Stream-K
+    worker, void/stream_k.py:166-193).  ``values`` [nnz, 32, 32] and ``b`` [K, N] are cast to fp32."""
+    nbr, nbc, row_ptr, bidx = _row_order(block_rows, block_cols, shape)
+    M, K = shape
+    N = b.shape[1]
+    a = np.asarray(values, dtype=np.float32)
+    bf = np.asarray(b, dtype=np.float32)
+    out = np.zeros((nbr * TILE, N), dtype=np.float32)
+    for r in range(nbr):
+        lo, hi = int(row_ptr[r]), int(row_ptr[r + 1])
+        if t_range is not None:
+            lo, hi = max(lo, t_range[0]), min(hi, t_range[1])
+        acc = np.zeros((TILE, N), dtype=np.float32)
+        for i in bidx[lo:hi]:
+            acc = acc + np.matmul(a[i], _b_block(bf, int(block_cols[i]), K))
+        out[r * TILE:(r + 1) * TILE] = acc
+    return out[:M]
+
+
 def spmm_int8_acc(values_q, block_rows, block_cols, shape, b_q, t_range=None):
     """int32 accumulators acc[nbr*32, N] = sum over the row's tiles of A_q . B_q, the tl.dot of
     void/int_quant.py:484-516.  float64 BLAS is exact here (|sum| < 2^53).  With t_range=(t0, t1)

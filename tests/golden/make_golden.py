@@ -17,6 +17,10 @@ Fixtures (all .npz, inputs included so that the tests do not depend on RNG stabi
   fp8_small.npz      FP8 quantisation (tiles and columns) and the FP8 SpMM kernel
   gelu_small.npz     fused GELU epilogue of the activation kernel (with and without bias)
   streamk_small.npz  Stream-K worker tables for a power-law row-length distribution
+  fp_small.npz       floating-point void_spmm (fp32 and fp16), void_spmv, fused GELU and the Stream-K
+                     kernel on a ragged matrix with empty tile rows
+
+A fixture whose arrays come out identical to the file already present is left untouched.
 """
 import os
 import sys
@@ -37,13 +41,21 @@ from void.fusion import void_spmm_activation_kernel  # noqa: E402
 from void.int_quant import (IntQuantConfig, ScaleMode, quantize_tensor, quantize_void_tensor,  # noqa: E402
                             void_spmm_int8)
 from void.ops import get_triton_dtype  # noqa: E402
-from void.stream_k import compute_stream_k_workload, analyze_workload_balance  # noqa: E402
+from void.ops import void_spmv_kernel  # noqa: E402
+from void.stream_k import compute_stream_k_workload, analyze_workload_balance, stream_k_spmm_kernel  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def save(name, **arrays):
     path = os.path.join(HERE, name)
+    if os.path.exists(path):
+        old = np.load(path)
+        if set(old.files) == set(arrays) and all(
+                old[k].dtype == np.asarray(v).dtype and np.array_equal(old[k], v, equal_nan=True)
+                for k, v in arrays.items()):
+            print("%-20s unchanged" % name)
+            return
     np.savez_compressed(path, **arrays)
     print("%-20s %7.1f KB" % (name, os.path.getsize(path) / 1024))
 
@@ -108,6 +120,35 @@ def ref_gelu_spmm(vt, b, bias):
         vt.values, vt.block_rows, vt.block_cols, row_ptr, block_indices, b, bias_t, out,
         M, N, K, vt.n_blocks, nbr, b.stride(0), b.stride(1), out.stride(0), out.stride(1), has_bias,
         TILE_M=vt.tile_size[0], TILE_K=vt.tile_size[1], TILE_N=TILE_N, ACTIVATION=2,
+        OUTPUT_DTYPE=get_triton_dtype(b.dtype))
+    return out
+
+
+def ref_spmv(vt, x):
+    """void_spmv without its CUDA assert, void/ops.py:320-347."""
+    out = torch.zeros(vt.shape[0], dtype=x.dtype)
+    row_ptr, block_indices = vt.get_row_block_info()
+    nbr = vt.block_grid[0]
+    void_spmv_kernel[(nbr,)](vt.values, vt.block_rows, vt.block_cols, row_ptr, block_indices, x, out,
+                             vt.shape[0], vt.shape[1], vt.n_blocks, nbr, TILE_M=vt.tile_size[0],
+                             TILE_K=vt.tile_size[1], OUTPUT_DTYPE=get_triton_dtype(x.dtype))
+    return out
+
+
+def ref_stream_k(vt, b, workload):
+    """void_spmm_stream_k without its CUDA assert, void/stream_k.py:262-299."""
+    M, K = vt.shape
+    N = b.shape[1]
+    tile_m, tile_k = vt.tile_size
+    out = torch.zeros(M, N, dtype=b.dtype)
+    _, block_indices = vt.get_row_block_info()
+    locks = torch.zeros(((M + tile_m - 1) // tile_m) * ((N + 63) // 64), dtype=torch.int32)
+    TILE_N = min(64, triton.next_power_of_2(N))
+    grid = (workload.n_workers, triton.cdiv(N, TILE_N))
+    stream_k_spmm_kernel[grid](
+        vt.values, vt.block_cols, block_indices, workload.worker_rows, workload.worker_block_start,
+        workload.worker_block_end, workload.worker_needs_atomic, b, out, locks, M, N, K, workload.n_workers,
+        b.stride(0), b.stride(1), out.stride(0), out.stride(1), TILE_M=tile_m, TILE_K=tile_k, TILE_N=TILE_N,
         OUTPUT_DTYPE=get_triton_dtype(b.dtype))
     return out
 
@@ -227,6 +268,24 @@ def main():
                                  bal["max_blocks_per_row"], bal["mean_blocks_per_row"], bal["std_blocks_per_row"],
                                  bal["imbalance_ratio"], bal["coefficient_of_variation"]], dtype=np.float64)
     save("streamk_small.npz", **out)
+
+    # ---------------------------------------------------------------- fp_small
+    rng = np.random.default_rng(23)
+    m = block_sparse_csr(rng, 7, 9, 0.45, M=200, K=270, empty_rows=(1, 4))
+    vt = void.csr_to_void(m, tile_size=32)
+    b = torch.from_numpy(rng.standard_normal((270, 80)).astype(np.float32))
+    bias = torch.from_numpy(rng.standard_normal(80).astype(np.float32))
+    x = torch.from_numpy(rng.standard_normal(270).astype(np.float32))
+    wl = compute_stream_k_workload(vt, n_workers=12, max_work_per_worker=2)
+    assert wl.worker_needs_atomic.any()
+    save("fp_small.npz", **coo_inputs(m), b=b.numpy(), bias=bias.numpy(), x=x.numpy(),
+         block_rows=vt.block_rows.numpy(), block_cols=vt.block_cols.numpy(),
+         c_fp32=void.void_spmm(vt, b).numpy(),
+         c_f16=void.void_spmm(vt.half(), b.half()).float().numpy(),
+         y_spmv=ref_spmv(vt, x).numpy(),
+         gelu=ref_gelu_spmm(vt, b, None).numpy(), gelu_bias=ref_gelu_spmm(vt, b, bias).numpy(),
+         stream_k=ref_stream_k(vt, b, wl).numpy(),
+         stream_k_meta=np.asarray([wl.n_workers, 12, 2], dtype=np.int64))
 
 
 if __name__ == "__main__":

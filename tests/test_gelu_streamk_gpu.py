@@ -62,10 +62,12 @@ def test_gelu_epilogue_fp8():
     assert rel_err(_np(c), vo.gelu_tanh_sigmoid(_np(pre))) < 1e-5
 
 
-def test_gelu_refuses_unquantised_tensor():
+def test_gelu_on_floating_tensor_matches_torch_tanh_gelu():
     w, _ = _zipf_tensor()
-    with pytest.raises(NotImplementedError):
-        void.void_spmm_gelu(w.a, w.b)
+    pre = void.void_spmm(w.a, w.b)
+    assert rel_err(_np(void.void_spmm_gelu(w.a, w.b)), _np(torch.nn.functional.gelu(pre, approximate="tanh"))) < 1e-5
+    with pytest.raises(TypeError):
+        void.void_spmm_gelu(object(), w.b)
 
 
 @pytest.mark.parametrize("tag", ["default", "w64", "w300_m4", "w7"])

@@ -65,6 +65,36 @@ def test_int8_spmm_c1():
     assert rel_err(c, a @ g["b"]) > 1e-3
 
 
+def test_fp_spmm_c1_and_small():
+    # the reference's fp32 void_spmm (void/ops.py:148-217) run through the Triton interpreter
+    g = load_golden("c1_plumbing.npz")
+    f = vo.csr_to_void_fields(coo_to_csr(g))
+    c = vo.spmm_fp(f["values"], f["block_rows"], f["block_cols"], f["shape"], g["b"])
+    assert rel_err(c, g["c_fp32"]) < 1e-6
+    assert rel_err(c, coo_to_csr(g).toarray() @ g["b"]) < 1e-5
+    g = load_golden("fp_small.npz")
+    f = vo.csr_to_void_fields(coo_to_csr(g))
+    assert np.array_equal(f["block_rows"], g["block_rows"]) and np.array_equal(f["block_cols"], g["block_cols"])
+    args = (f["values"], f["block_rows"], f["block_cols"], f["shape"])
+    c = vo.spmm_fp(*args, g["b"])
+    assert c.shape == (200, 80) and rel_err(c, g["c_fp32"]) < 1e-6
+    assert not c[32:64].any() and not c[128:160].any()                    # empty tile rows stay zero
+    assert rel_err(vo.spmm_fp(*args, g["x"][:, None])[:, 0], g["y_spmv"]) < 1e-6
+    assert rel_err(vo.gelu_tanh_sigmoid(c), g["gelu"]) < 1e-6
+    assert rel_err(vo.gelu_tanh_sigmoid(c + g["bias"][None, :]), g["gelu_bias"]) < 1e-6
+    # fp16 tiles and fp16 B: products in fp32, result rounded to fp16 once
+    c16 = vo.spmm_fp(f["values"].astype(np.float16), *args[1:], g["b"].astype(np.float16))
+    assert rel_err(c16.astype(np.float16).astype(np.float32), g["c_f16"]) < 1e-3
+    # Stream-K: the sum of the workers' partial products is the plain product (void/stream_k.py:198-219)
+    rp, _ = vo.row_block_info(f["block_rows"], f["block_cols"], 7, 9)
+    rows, start, end, atomic = vo.stream_k_workload(rp, len(f["block_rows"]), 12, 2)
+    assert len(rows) == int(g["stream_k_meta"][0]) and atomic.any()
+    total = np.zeros_like(c)
+    for r, t0, t1 in zip(rows, start, end):
+        total[r * 32:(r + 1) * 32] += vo.spmm_fp(*args, g["b"], t_range=(int(t0), int(t1)))[r * 32:(r + 1) * 32]
+    assert rel_err(total, g["stream_k"]) < 1e-6 and rel_err(g["stream_k"], g["c_fp32"]) < 1e-6
+
+
 def test_int8_spmm_small_cases():
     g = load_golden("int8_small.npz")
     shape = tuple(int(x) for x in g["shape"])

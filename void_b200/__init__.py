@@ -1,7 +1,7 @@
 """void_b200 - the quantized block-sparse SpMM path of VOID, rebuilt for B200 (sm_100a).
 
 Same names as the reference's ``void`` package for everything on that path, so
-``import void_b200 as void`` is a drop-in for: csr_to_void, quantize_void_tensor, void_spmm_int8,
+``import void_b200 as void`` is a drop-in for: csr_to_void, void_spmm, quantize_void_tensor, void_spmm_int8,
 void_tensor_to_fp8 / void_spmm_fp8, void_spmm_gelu, compute_stream_k_workload /
 void_spmm_stream_k, shard_void_tensor / distributed_void_spmm.  All arithmetic runs in
 hand-written CUDA behind a C ABI (include/void_b200.h); there is no Triton, no dispatch layer and
@@ -14,6 +14,7 @@ from .int_quant import (IntFormat, ScaleMode, IntQuantConfig, QuantizationParams
                         get_quantization_error, quantize_cols_int8)
 from .fp8 import (FP8Format, FP8Config, FP8ScalingInfo, FP8VOIDTensor, create_scaling_info, compute_amax,
                   quantize_to_fp8, dequantize_from_fp8, void_spmm_fp8, void_tensor_to_fp8, quantize_cols_fp8)
+from .ops import void_spmm, void_spmv
 from .fusion import ActivationType, get_activation_code, void_spmm_gelu, void_spmm_relu, void_spmm_silu
 from .stream_k import (StreamKWorkload, compute_stream_k_workload, void_spmm_stream_k, analyze_workload_balance)
 from .scheduler import WorkloadProfile, analyze_workload

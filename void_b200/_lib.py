@@ -17,7 +17,9 @@ _LIB = None
 c_i32, c_i64, c_f32, c_vp, c_sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 
 # enums of include/void_b200.h
-KIND_I8, KIND_F8E4M3 = 0, 1
+KIND_I8, KIND_F8E4M3, KIND_F16, KIND_BF16, KIND_TF32 = 0, 1, 2, 3, 4
+FP_KIND = {torch.float16: KIND_F16, torch.bfloat16: KIND_BF16, torch.float32: KIND_TF32}
+KIND_ELEM_BYTES = {KIND_I8: 1, KIND_F8E4M3: 1, KIND_F16: 2, KIND_BF16: 2, KIND_TF32: 4}
 OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 SCALE_ROW_MEAN, SCALE_PER_TILE = 0, 1
@@ -49,6 +51,7 @@ _PROTOTYPES = {
     "void_tile_index_ws_bytes": (c_sz, [c_i32, c_i32]),
     "void_build_tile_index": (ctypes.c_int, [c_vp, c_vp, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "void_pack_tiles": (ctypes.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "void_pack_tiles_fp": (ctypes.c_int, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_i8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_fp8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "void_quant_cols": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp, c_vp]),
@@ -62,6 +65,7 @@ _PROTOTYPES = {
     "void_plan_segments_host": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "void_spmm_i8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
     "void_spmm_f8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
+    "void_spmm_fp": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_i32, c_vp]),
     "void_spmm_i8_static_scratch": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_i32, c_vp]),
 }
 

@@ -24,9 +24,9 @@ def _aligned_empty(nbytes: int, device, align: int = 1024) -> torch.Tensor:
 
 @dataclass
 class PackedTiles:
-    """A in the layout the kernels stream: tiles in tile-row-major order, 1024 bytes each, already
+    """A in the layout the kernels stream: tiles in tile-row-major order, 1024 elements each, already
     in the tensor cores' core-matrix order, with per-tile column index and scale."""
-    tiles: torch.Tensor        # uint8 [nnz * 1024], 1024-byte aligned
+    tiles: torch.Tensor        # uint8 [nnz * 1024 * element bytes], 1024-byte aligned
     tile_cols: torch.Tensor    # int32 [nnz]
     tile_scales: torch.Tensor  # float32 [nnz]
     row_ptr: torch.Tensor      # int32 [nbr + 1]
@@ -42,7 +42,8 @@ class PackedTiles:
 
 def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch.Tensor, block_cols: torch.Tensor,
          shape, kind: int, row_ptr=None, block_indices=None) -> PackedTiles:
-    """Build the packed store of an 8-bit VOID tensor on its device (void_pack_tiles)."""
+    """Build the packed store of a VOID tensor on its device: void_pack_tiles for the 8-bit kinds,
+    void_pack_tiles_fp for fp16 / bf16 / fp32 tiles (no scales)."""
     from .format import build_tile_index
     _lib.require_cuda(values, block_rows, block_cols)
     lib = _lib.load()
@@ -50,19 +51,26 @@ def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch
     M, K = shape
     nbr, nbc = (M + TILE - 1) // TILE, (K + TILE - 1) // TILE
     nnz = values.shape[0]
-    if values.dim() != 3 or values.shape[1] != TILE or values.shape[2] != TILE or values.element_size() != 1:
-        raise _lib.VoidB200Error("void_b200 kernels need 32x32 tiles of 8-bit elements, got %s %s"
-                                 % (tuple(values.shape), values.dtype))
+    es = _lib.KIND_ELEM_BYTES[kind]
+    if values.dim() != 3 or values.shape[1] != TILE or values.shape[2] != TILE or values.element_size() != es:
+        raise _lib.VoidB200Error("void_b200 kernels need 32x32 tiles of %d-byte elements here, got %s %s"
+                                 % (es, tuple(values.shape), values.dtype))
     with torch.cuda.device(dev):
         if row_ptr is None or block_indices is None:
             row_ptr, block_indices = build_tile_index(block_rows, block_cols, nbr, nbc)
         vals = values.contiguous()
-        tiles = _aligned_empty(max(nnz, 1) * 1024, dev)
+        tiles = _aligned_empty(max(nnz, 1) * 1024 * es, dev)
         tile_cols = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)
         tile_scales = torch.empty(max(nnz, 1), dtype=torch.float32, device=dev)
         row_scale = torch.empty(max(nbr, 1), dtype=torch.float32, device=dev)
         sc = None if scales is None else scales.contiguous().to(torch.float32).reshape(-1)
         bc = block_cols.contiguous().to(torch.int32)
+        if es > 1:
+            _lib.check(lib.void_pack_tiles_fp(_lib.ptr(vals), es, _lib.ptr(bc), _lib.ptr(block_indices), nnz,
+                                              _lib.ptr(tiles), _lib.ptr(tile_cols), _lib.stream_ptr(dev)),
+                       "void_pack_tiles_fp")
+            return PackedTiles(tiles, tile_cols, tile_scales, row_ptr, block_indices, row_scale, nbr, nbc, nnz,
+                               (M, K), kind)
         _lib.check(lib.void_pack_tiles(_lib.ptr(vals), _lib.ptr(sc), 0 if sc is None else sc.numel(), _lib.ptr(bc),
                                        _lib.ptr(block_indices), _lib.ptr(row_ptr), nnz, nbr, _lib.ptr(tiles),
                                        _lib.ptr(tile_cols), _lib.ptr(tile_scales), _lib.ptr(row_scale),
@@ -73,7 +81,7 @@ def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch
 
 def cached_pack(owner, values, scales, block_rows, block_cols, shape, kind) -> PackedTiles:
     """Packed store cached on the tensor object, rebuilt when its storage or contents change."""
-    key = (values.data_ptr(), values._version, None if scales is None else (scales.data_ptr(), scales._version),
+    key = (kind, values.data_ptr(), values._version, None if scales is None else (scales.data_ptr(), scales._version),
            block_rows.data_ptr(), block_cols.data_ptr(), str(values.device), tuple(shape))
     p = getattr(owner, "_packed_cache", None)
     if p is None or p.key != key:
@@ -171,13 +179,14 @@ def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chun
                 chunk_tiles)
 
 
-def prepare_b(b: torch.Tensor) -> torch.Tensor:
-    """B as the kernels need it: 8-bit, row-major, 16-byte aligned rows (the copy engine's rule)."""
-    if b.element_size() != 1:
-        raise _lib.VoidB200Error("B must be 8-bit (int8 / float8_e4m3fn), got %s" % b.dtype)
-    if b.stride(1) != 1 or b.stride(0) % 16 != 0 or b.data_ptr() % 16 != 0 or b.stride(0) < b.shape[1]:
+def prepare_b(b: torch.Tensor, elem_bytes: int = 1) -> torch.Tensor:
+    """B as the kernels need it: row-major, rows starting on 16-byte boundaries (the copy engine's rule)."""
+    if b.element_size() != elem_bytes:
+        raise _lib.VoidB200Error("B must have %d-byte elements to match A, got %s" % (elem_bytes, b.dtype))
+    per16 = 16 // elem_bytes
+    if b.stride(1) != 1 or b.stride(0) % per16 != 0 or b.data_ptr() % 16 != 0 or b.stride(0) < b.shape[1]:
         K, N = b.shape
-        ld = (N + 15) // 16 * 16
+        ld = (N + per16 - 1) // per16 * per16
         padded = torch.zeros(K, ld, dtype=b.dtype, device=b.device)
         padded[:, :N] = b
         b = padded[:, :N]
@@ -188,7 +197,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
          grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None) -> torch.Tensor:
-    """One launch of void_spmm_i8 / void_spmm_f8 on the current stream of b's device."""
+    """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
     dev = b.device
@@ -200,15 +209,16 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
         raise _lib.VoidB200Error("out must be a row-major [%d, %d] tensor" % (M, N))
     if out.dtype not in _lib.OUT_DTYPE_CODE:
         raise _lib.VoidB200Error("unsupported output dtype %s" % out.dtype)
-    b = prepare_b(b)
+    es = _lib.KIND_ELEM_BYTES[packed.kind]
+    b = prepare_b(b, es)
     a = _lib.SpmmArgs()
     a.tiles = packed.tiles.data_ptr()
     a.tile_cols = packed.tile_cols.data_ptr()
     a.tile_scales = packed.tile_scales.data_ptr()
     a.row_ptr = packed.row_ptr.data_ptr()
-    a.row_scale = packed.row_scale.data_ptr() if (use_row_scale and scale_mode == _lib.SCALE_ROW_MEAN) else None
+    a.row_scale = packed.row_scale.data_ptr() if (use_row_scale and scale_mode == _lib.SCALE_ROW_MEAN and es == 1) else None
     a.nbr, a.nbc, a.nnz = packed.nbr, packed.nbc, packed.nnz
-    a.b, a.ldb, a.K, a.N = b.data_ptr(), b.stride(0), K, N
+    a.b, a.ldb, a.K, a.N = b.data_ptr(), b.stride(0) * es, K, N
     keep = [b]
     if col_scale is not None:
         col_scale = col_scale.to(device=dev, dtype=torch.float32).contiguous()
@@ -235,7 +245,10 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     a.panels_per_item, a.stages, a.grid, a.tiles_per_stage = panels_per_item, stages, grid, tiles_per_stage
     a.trace = None if trace is None else trace.data_ptr()
     a.cta_shape = cta_shape
-    fn = lib.void_spmm_i8 if packed.kind == _lib.KIND_I8 else lib.void_spmm_f8
     with torch.cuda.device(dev):
-        _lib.check(fn(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm")
+        if es > 1:
+            _lib.check(lib.void_spmm_fp(ctypes.byref(a), packed.kind, _lib.stream_ptr(dev)), "void_spmm_fp")
+        else:
+            fn = lib.void_spmm_i8 if packed.kind == _lib.KIND_I8 else lib.void_spmm_f8
+            _lib.check(fn(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm")
     return out

@@ -94,6 +94,31 @@ __global__ void pack_tiles_kernel(const uint4* __restrict__ values, const int32_
   packed[g] = values[src_tile * 64 + r * 2 + c16];
 }
 
+// The same for elements of ES bytes: a tile row holds KC = 2*ES 16-byte chunks, a packed tile
+// 64*ES of them in the order [row / 8][chunk][row % 8].
+template <int ES>
+__global__ void pack_tiles_fp_kernel(const uint4* __restrict__ values, const int32_t* __restrict__ block_indices,
+                                     int64_t nnz, uint4* __restrict__ packed) {
+  constexpr int KC = 2 * ES, PER_TILE = 64 * ES;
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= nnz * PER_TILE) return;
+  const int64_t j = g / PER_TILE;
+  const int q = (int)(g - j * PER_TILE);
+  const int r = (q / (8 * KC)) * 8 + (q & 7);
+  const int kc = (q >> 3) % KC;
+  const int64_t src_tile = block_indices[j];
+  uint4 v = values[src_tile * PER_TILE + r * KC + kc];
+  if (ES == 4) {
+    // The tensor cores read an fp32 operand as TF32 by dropping its low 13 mantissa bits.  Rounding the
+    // tiles to the nearest TF32 value here, once, halves the error of that and removes its bias.
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v.x) : "f"(__uint_as_float(v.x)));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v.y) : "f"(__uint_as_float(v.y)));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v.z) : "f"(__uint_as_float(v.z)));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v.w) : "f"(__uint_as_float(v.w)));
+  }
+  packed[g] = v;
+}
+
 __global__ void gather_tile_meta_kernel(const int32_t* __restrict__ bcol, const float* __restrict__ scales,
                                         int64_t n_scales, const int32_t* __restrict__ block_indices, int64_t nnz,
                                         int32_t* __restrict__ tile_cols, float* __restrict__ tile_scales) {
@@ -373,6 +398,28 @@ int void_pack_tiles(const void* values, const float* scales, int64_t n_scales, c
     if (row_ptr == nullptr || (nnz > 0 && tile_scales == nullptr)) return VOID_ERR_BAD_ARG;
     row_scale_kernel<<<(nbr + tb - 1) / tb, tb, 0, st>>>(row_ptr, tile_scales, nbr, row_scale);
   }
+  return last_status();
+}
+
+int void_pack_tiles_fp(const void* values, int32_t elem_bytes, const int32_t* block_cols, const int32_t* block_indices,
+                       int64_t nnz, void* packed, int32_t* tile_cols, void_stream_t stream) {
+  if (nnz < 0 || (elem_bytes != 2 && elem_bytes != 4)) return VOID_ERR_BAD_ARG;
+  if (nnz == 0) return VOID_OK;
+  if (values == nullptr || block_cols == nullptr || block_indices == nullptr || packed == nullptr || tile_cols == nullptr)
+    return VOID_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(values) & 15u) != 0 || (reinterpret_cast<uintptr_t>(packed) & 1023u) != 0)
+    return VOID_ERR_ALIGN;
+  cudaStream_t st = as_stream(stream);
+  const int tb = 256;
+  const unsigned blocks = (unsigned)((nnz * 64 * elem_bytes + tb - 1) / tb);
+  if (elem_bytes == 2)
+    pack_tiles_fp_kernel<2><<<blocks, tb, 0, st>>>(reinterpret_cast<const uint4*>(values), block_indices, nnz,
+                                                   reinterpret_cast<uint4*>(packed));
+  else
+    pack_tiles_fp_kernel<4><<<blocks, tb, 0, st>>>(reinterpret_cast<const uint4*>(values), block_indices, nnz,
+                                                   reinterpret_cast<uint4*>(packed));
+  gather_tile_meta_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_cols, nullptr, 0, block_indices, nnz,
+                                                                         tile_cols, nullptr);
   return last_status();
 }
 

@@ -133,6 +133,30 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 16-bit floating operands (fp16 or bf16, named by the instruction descriptor), fp32 accumulator; K = 16.
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// fp32 operands read as TF32 (low 13 mantissa bits ignored), fp32 accumulator; K = 8.
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Same with FP8/FP6/FP4 operands (E4M3 here), fp32 accumulator.
 __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                        uint32_t accumulate) {
@@ -184,7 +208,7 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor (64 bit): start address, leading / stride byte offsets
 // (all >> 4), descriptor version 1 for sm_100, layout type in the top three bits.
-constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2, kLayoutSw64 = 4, kLayoutSw32 = 6;
+constexpr uint32_t kLayoutNone = 0, kLayoutSw128Base32 = 1, kLayoutSw128 = 2, kLayoutSw64 = 4, kLayoutSw32 = 6;
 __host__ __device__ constexpr uint64_t smem_desc_hi(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   return (uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32) |
          (uint64_t(1) << 46) | (uint64_t(layout & 7u) << 61);

@@ -48,6 +48,13 @@ constexpr int kTile = 32;
 constexpr int kTileBytes = 1024;
 constexpr int kPanelN = 128;
 constexpr int kPanelBytes = kTile * kPanelN;  // 4096
+// Bytes per element of the operands of a kind: the 8-bit kinds, fp16 / bf16, fp32 read as TF32.  A tile
+// takes kTileBytes * ES bytes, a 128-column panel kPanelBytes * ES (stored as ES blocks of 32 k-rows x
+// 128 bytes, one swizzle atom wide each), and one (tile, panel) product takes ES MMAs of 32 bytes of k.
+template <int KIND>
+struct Elem {
+  static constexpr int ES = (KIND == VOID_KIND_TF32) ? 4 : ((KIND == VOID_KIND_F16 || KIND == VOID_KIND_BF16) ? 2 : 1);
+};
 constexpr int kMaxStages = 16;
 constexpr int kMaxSlots = 16;
 // Warp roles of a CTA: PW producer warps (0..PW-1) stream tiles and panels, warp PW issues the MMAs
@@ -276,16 +283,18 @@ struct __align__(8) PipeBars {
 };
 
 // shared-memory offsets inside one ring stage
+template <int ES>
 __device__ __forceinline__ uint32_t panel_off(const SpmmParams& p, int j, int q) {
-  return (uint32_t)(j * p.np + q) * kPanelBytes;
+  return (uint32_t)(j * p.np + q) * (kPanelBytes * ES);
 }
+template <int ES>
 __device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
-  return (uint32_t)(p.group * p.np) * kPanelBytes + (uint32_t)j * kTileBytes;
+  return (uint32_t)(p.group * p.np) * (kPanelBytes * ES) + (uint32_t)j * (kTileBytes * ES);
 }
 
 // Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
 // consumes them; group g uses ring stage g % stages and belongs to warp g % C::PW.
-template <class C>
+template <class C, int ES>
 __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtensorMap* tmap, PipeBars* bars,
                                               uint32_t ring_base, uint32_t stage_bytes, volatile int* abort_flag,
                                               int lane, int pw) {
@@ -300,7 +309,7 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     if (i + step < end) seg_next = load_seg(p, i + step);
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
-    const uint32_t unit_bytes = (uint32_t)(kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes);
+    const uint32_t unit_bytes = (uint32_t)((kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes) * ES);
     const int ngroups = (s.t1 - s.t0 + G - 1) / G;
     int k = pw - g % C::PW;
     if (k < 0) k += C::PW;
@@ -323,17 +332,20 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
         ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag) ? 1 : 0;
         if (ok) {
           mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
-          bulk_load(sbase + tile_off(p, 0), p.tiles + (size_t)t * kTileBytes, (uint32_t)gcnt * kTileBytes, full);
+          bulk_load(sbase + tile_off<ES>(p, 0), p.tiles + (size_t)t * (kTileBytes * ES),
+                    (uint32_t)gcnt * (kTileBytes * ES), full);
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
       if (lane < gcnt) {
         if (p.use3d) {
-          tma_load_3d(sbase + panel_off(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np, full);
+          tma_load_3d(sbase + panel_off<ES>(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np * ES, full);
         } else {
-          for (int q = 0; q < npan; ++q)
-            tma_load_2d(sbase + panel_off(p, lane, q), tmap, n0 + q * kPanelN, col * kTile, full);
+          // one copy per 128-byte-wide block of columns: ES blocks of 128 / ES columns per panel
+          for (int q = 0; q < npan * ES; ++q)
+            tma_load_2d(sbase + panel_off<ES>(p, lane, 0) + (uint32_t)q * kPanelBytes, tmap,
+                        n0 + q * (kPanelN / ES), col * kTile, full);
         }
       }
       if (lane == 0 && p.trace != nullptr && i == begin && k < 16) stamp(p, 32 + k);
@@ -346,7 +358,9 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
 template <int KIND>
 __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   if (KIND == VOID_KIND_I8) mma_i8(d, a, b, idesc, acc);
-  else mma_f8(d, a, b, idesc, acc);
+  else if (KIND == VOID_KIND_F8E4M3) mma_f8(d, a, b, idesc, acc);
+  else if (KIND == VOID_KIND_TF32) mma_tf32(d, a, b, idesc, acc);
+  else mma_f16(d, a, b, idesc, acc);
 }
 
 template <class C>
@@ -416,7 +430,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes));
+  constexpr int ES = Elem<KIND>::ES;
+  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes) * ES);
   const uint32_t acc_cols = (uint32_t)p.np * 32u;  // TMEM columns of one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
@@ -427,7 +442,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
-    producer_loop<C>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+    producer_loop<C, ES>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
     if (warp == 0 && lane == 0) stamp(p, 2);
   } else if (warp == C::MMA) {
     if (lane == 0) {
@@ -437,8 +452,11 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
       const int G = p.group, S = p.stages, np = p.np;
-      const uint32_t tiles_at = (uint32_t)(G * np) * kPanelBytes;
-      constexpr uint64_t kPanelStep = kPanelBytes >> 4, kTileStep = kTileBytes >> 4;
+      const uint32_t tiles_at = (uint32_t)(G * np) * (kPanelBytes * ES);
+      constexpr uint64_t kPanelStep = (kPanelBytes * ES) >> 4, kTileStep = (kTileBytes * ES) >> 4;
+      // one MMA covers 32 bytes of k: 32 / ES k-rows of the panel (8-row groups 1024 bytes apart) and two
+      // 16-byte k-chunks of the packed tile (128 bytes apart)
+      constexpr uint64_t kPanelKStep = (kPanelBytes / ES) >> 4, kTileKStep = 256 >> 4;
       int begin, end, step;
       seg_range(p, begin, end, step);
       int stage = 0;
@@ -473,6 +491,9 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             uint32_t d = d0;
             for (int q = 0; q < npan; ++q) {
               issue_mma<KIND>(d, adq, bd, idesc, acc);
+#pragma unroll
+              for (int kk = 1; kk < ES; ++kk)
+                issue_mma<KIND>(d, adq + kk * kPanelKStep, bd + kk * kTileKStep, idesc, 1u);
               adq += kPanelStep;
               d += 32u;
             }
@@ -590,7 +611,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             int32_t* dst = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
                            (quad * 32 + lane);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
+            for (int k = 0; k < 8; ++k) {
+              if (KIND == VOID_KIND_I8) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
+              else atomicAdd(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
+            }
           }
         }
         cs = cs_next;
@@ -682,7 +706,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
-    producer_loop<C>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+    producer_loop<C, 1>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
     if (warp == 0 && lane == 0) stamp(p, 2);
   } else if (warp == C::MMA) {
     if (lane == 0) {
@@ -912,7 +936,12 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if ((long long)a->nbr * kTile < a->M) return VOID_ERR_SHAPE;
   if (a->ldc < a->N) return VOID_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(a->tiles) & 1023u) != 0) return VOID_ERR_ALIGN;
-  if ((reinterpret_cast<uintptr_t>(a->b) & 15u) != 0 || (a->ldb & 15) != 0 || a->ldb < a->N) return VOID_ERR_ALIGN;
+  if (kind < VOID_KIND_I8 || kind > VOID_KIND_TF32) return VOID_ERR_BAD_ARG;
+  const int es = (kind == VOID_KIND_TF32) ? 4 : ((kind == VOID_KIND_F16 || kind == VOID_KIND_BF16) ? 2 : 1);
+  const bool floating = es > 1;
+  if ((reinterpret_cast<uintptr_t>(a->b) & 15u) != 0 || (a->ldb & 15) != 0 || a->ldb < (long long)a->N * es)
+    return VOID_ERR_ALIGN;
+  if (floating && (a->scale_mode != VOID_SCALE_ROW_MEAN || a->row_scale != nullptr)) return VOID_ERR_BAD_ARG;
 
   const DeviceInfo dev = device_info();
   if (!dev.ok) return VOID_ERR_CUDA;
@@ -922,6 +951,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   const int total_panels = (a->N + kPanelN - 1) / kPanelN;
   int np = a->panels_per_item;
   if (np != 0 && np != 1 && np != 2 && np != 4) return VOID_ERR_BAD_ARG;
+  if (floating && np > 2) return VOID_ERR_BAD_ARG;  // ring stages of wider items do not fit
+  if (np == 0 && floating) np = 1;
   if (np == 0) {
     // two panels per item keep two CTAs on an SM, which measured faster than four panels with one
     np = total_panels >= 2 ? 2 : 1;
@@ -942,11 +973,12 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   const int ctas_per_sm = slim ? Slim::CTAS_PER_SM : ((np == 4) ? 1 : Wide::CTAS_PER_SM);
   int group = a->tiles_per_stage;  // 0 = default
   if (group == 0) group = (np == 1) ? 4 : 2;  // few, large ring stages beat a deep ring of small ones
+  if (a->tiles_per_stage == 0 && floating) group = (es == 2 && np == 1) ? 2 : 1;
   if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
   if (drain && slim && a->tiles_per_stage == 0) group = 2;
   const int drain_tmem = 512 / ctas_per_sm;
   if (drain && group * np * 32 * 2 > drain_tmem) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
-  const int stage_bytes = group * (np * kPanelBytes + kTileBytes);
+  const int stage_bytes = group * (np * kPanelBytes + kTileBytes) * es;
   int stages = a->stages;
   if (stages == 0) {
     const int budget = (216 * 1024) / ctas_per_sm - 2048;
@@ -988,7 +1020,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.np = np;
   p.group = group;
   p.stages = stages;
-  p.use3d = (a->N % kPanelN == 0) ? 1 : 0;
+  p.use3d = (a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
   p.n_items = a->nbr * n_chunks;
 
@@ -997,14 +1029,27 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   // (stride offset).  B panel (operand A, MN-major, 128-byte swizzle): one swizzle atom along n,
   // four 8-row groups along k, 1024 bytes apart.
   p.desc_hi_b = smem_desc_hi(128, 256, kLayoutNone);
-  p.desc_hi_a = smem_desc_hi(1024, 1024, kLayoutSw128);
+  // Wider elements: the tile's row groups are 256 * es bytes apart; the panel is es swizzle atoms wide
+  // along n, 4096 bytes apart (leading offset), its 8-row k groups stay 1024 bytes apart.
+  // 32-bit elements in an MN-major operand need the swizzle that permutes 32-byte pieces of a 128-byte
+  // row (pattern of 4 rows, so k groups of 4 rows, 512 bytes apart); the copy engine writes the same
+  // pattern with its 32-byte-atom mode.
+  if (floating) {
+    p.desc_hi_b = smem_desc_hi(128, 256 * es, kLayoutNone);
+    p.desc_hi_a = (es == 4) ? smem_desc_hi(4096, 512, kLayoutSw128Base32) : smem_desc_hi(4096, 1024, kLayoutSw128);
+  } else {
+    p.desc_hi_a = smem_desc_hi(1024, 1024, kLayoutSw128);
+  }
   if (kind == VOID_KIND_I8) p.idesc = instr_desc(/*c s32*/ 2, /*a s8*/ 1, /*b s8*/ 1, /*a MN*/ 1, /*b K*/ 0, 128, 32);
-  else p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, 1, 0, 128, 32);
+  else if (kind == VOID_KIND_F8E4M3) p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, 1, 0, 128, 32);
+  else if (kind == VOID_KIND_F16) p.idesc = instr_desc(1, /*a f16*/ 0, /*b f16*/ 0, 1, 0, 128, 32);
+  else if (kind == VOID_KIND_BF16) p.idesc = instr_desc(1, /*a bf16*/ 1, /*b bf16*/ 1, 1, 0, 128, 32);
+  else p.idesc = instr_desc(1, /*a tf32*/ 2, /*b tf32*/ 2, 1, 0, 128, 32);
 
   int grid;
   if (a->segs != nullptr) {
     if (a->cta_seg_ptr == nullptr || a->n_cta <= 0 || a->panels_per_item == 0) return VOID_ERR_BAD_ARG;
-    if (drain || kind != VOID_KIND_I8) return VOID_ERR_BAD_ARG;  // split rows: int32 row-accumulate kernel only
+    if (drain || kind == VOID_KIND_F8E4M3) return VOID_ERR_BAD_ARG;  // split rows: row-accumulate kernel only
     grid = a->n_cta;
   } else {
     grid = a->grid > 0 ? a->grid : dev.sms * ctas_per_sm;
@@ -1021,23 +1066,28 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
     if (enc == nullptr) return VOID_ERR_CUDA;
     CUresult r = CUDA_ERROR_INVALID_VALUE;
+    // elements of es bytes: every box is 128 bytes (kPanelN / es columns) wide, a panel takes es of them
+    const CUtensorMapDataType dt = (es == 1) ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : (es == 2) ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    const int box_n = kPanelN / es;
+    const CUtensorMapSwizzle swz = (es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     if (p.use3d) {
-      const cuuint64_t gdim[3] = {(cuuint64_t)kPanelN, (cuuint64_t)a->K, (cuuint64_t)total_panels};
+      const cuuint64_t gdim[3] = {(cuuint64_t)box_n, (cuuint64_t)a->K, (cuuint64_t)(a->N / box_n)};
       const cuuint64_t gstride[2] = {(cuuint64_t)a->ldb, (cuuint64_t)kPanelN};
-      const cuuint32_t box[3] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile, (cuuint32_t)np};
+      const cuuint32_t box[3] = {(cuuint32_t)box_n, (cuuint32_t)kTile, (cuuint32_t)(np * es)};
       const cuuint32_t estride[3] = {1, 1, 1};
-      r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(a->b), gdim, gstride, box, estride,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      r = enc(&tmap, dt, 3, const_cast<void*>(a->b), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) p.use3d = 0;  // fall back to one 2-D copy per panel
     }
     if (!p.use3d) {
       const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->K};
       const cuuint64_t gstride[1] = {(cuuint64_t)a->ldb};
-      const cuuint32_t box[2] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile};
+      const cuuint32_t box[2] = {(cuuint32_t)box_n, (cuuint32_t)kTile};
       const cuuint32_t estride[2] = {1, 1};
-      r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(a->b), gdim, gstride, box, estride,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      r = enc(&tmap, dt, 2, const_cast<void*>(a->b), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) return VOID_ERR_TENSOR_MAP;
@@ -1048,7 +1098,15 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
     launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, p);                    \
   } while (0)
-  if (!drain) {
+  if (floating) {
+    if (kind == VOID_KIND_TF32) {
+      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Slim>), Slim);
+      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Wide>), Wide);
+    } else {  // fp16 and bf16 differ in the instruction descriptor only
+      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Slim>), Slim);
+      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Wide>), Wide);
+    }
+  } else if (!drain) {
     if (kind == VOID_KIND_I8) {
       if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
       else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Wide>), Wide);
@@ -1135,6 +1193,10 @@ int void_spmm_i8(const void_spmm_args* args, void_stream_t stream) {
 }
 int void_spmm_f8(const void_spmm_args* args, void_stream_t stream) {
   return vb::spmm_launch(args, VOID_KIND_F8E4M3, reinterpret_cast<cudaStream_t>(stream));
+}
+int void_spmm_fp(const void_spmm_args* args, int32_t kind, void_stream_t stream) {
+  if (kind != VOID_KIND_F16 && kind != VOID_KIND_BF16 && kind != VOID_KIND_TF32) return VOID_ERR_BAD_ARG;
+  return vb::spmm_launch(args, kind, reinterpret_cast<cudaStream_t>(stream));
 }
 int void_device_sm_count(void) {
   const vb::DeviceInfo d = vb::device_info();

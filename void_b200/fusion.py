@@ -6,9 +6,9 @@ Mirrors ActivationType / get_activation_code (void/fusion.py:21-32, :77-91) and 
 applied to the dequantised fp32 accumulator (plus the column bias, :179-183) inside the SpMM
 kernel's epilogue, before the fp16 / bf16 store.
 
-The reference's void_spmm_gelu takes a floating-point VOIDTensor.  The B200 path is the quantized
-one, so ``a`` is an Int8VOIDTensor or FP8VOIDTensor here; a floating-point VOIDTensor is refused
-rather than silently quantised.
+The reference's void_spmm_gelu takes a floating-point VOIDTensor (TF32 product, result cast to B's
+dtype, void/fusion.py:186-189); that form runs through void_spmm's kernel.  An Int8VOIDTensor or
+FP8VOIDTensor selects the quantized kernels with the same epilogue.
 """
 from enum import Enum
 from typing import Optional, Union
@@ -16,8 +16,10 @@ from typing import Optional, Union
 import torch
 
 from . import _lib
+from .format import VOIDTensor
 from .fp8 import FP8VOIDTensor, void_spmm_fp8
 from .int_quant import Int8VOIDTensor, void_spmm_int8
+from .ops import void_spmm
 
 
 class ActivationType(Enum):
@@ -46,15 +48,19 @@ def _void_spmm_activation(a, b, bias, out, activation: str, **kw) -> torch.Tenso
         return void_spmm_int8(a, b, kw.pop("b_scale", None), out, out_dtype=out_dtype, activation=code, bias=bias, **kw)
     if isinstance(a, FP8VOIDTensor):
         return void_spmm_fp8(a, b, kw.pop("output_dtype", torch.float16), out=out, activation=code, bias=bias, **kw)
-    raise NotImplementedError(
-        "void_b200 fuses the activation into the quantized SpMM: pass an Int8VOIDTensor "
-        "(quantize_void_tensor) or an FP8VOIDTensor (void_tensor_to_fp8), got %s" % type(a).__name__)
+    if isinstance(a, VOIDTensor):
+        if kw:
+            raise TypeError("unexpected keyword arguments for a floating-point VOIDTensor: %s" % sorted(kw))
+        assert bias is None or bias.shape == (b.shape[1],), "bias must be a vector of N columns"   # void/fusion.py:452
+        return void_spmm(a, b, out, activation=code, bias=bias)
+    raise TypeError("void_spmm activation kernels take a VOIDTensor, Int8VOIDTensor or FP8VOIDTensor, got %s"
+                    % type(a).__name__)
 
 
 def void_spmm_gelu(a, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                    **kw) -> torch.Tensor:
-    """C = GELU(A @ B + bias) in one kernel (void/fusion.py:381-399).  Keyword extensions:
-    ``b_scale`` / ``out_dtype`` (INT8) or ``b_scale`` / ``output_dtype`` (FP8)."""
+    """C = GELU(A @ B + bias) in one kernel (void/fusion.py:381-399).  Keyword extensions for the
+    quantized tensors: ``b_scale`` / ``out_dtype`` (INT8) or ``b_scale`` / ``output_dtype`` (FP8)."""
     return _void_spmm_activation(a, b, bias, out, "gelu", **kw)
 
 

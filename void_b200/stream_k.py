@@ -7,9 +7,11 @@ The worker table is the reference's, bit for bit, but it is built by a device ke
 Python loop with one .item() per row (:76-97).  The SpMM differs in how partial rows are joined:
 the reference lets every partial worker lock the output tile and read-modify-write it in the
 output dtype (:198-219, an unbounded spin); here consecutive workers of a row that land on the
-same CTA keep accumulating in tensor memory, rows that are shared between CTAs park int32
-partial sums, and the CTA that arrives last adds them and runs the epilogue - no lock, no wait,
-and an exact (integer) sum that does not depend on arrival order.
+same CTA keep accumulating in tensor memory, rows that are shared between CTAs add their partial
+sums into one accumulator per row with atomic adds, and the CTA that arrives last reads it back
+and runs the epilogue - no lock and no wait.  For an Int8VOIDTensor the sums are int32, exact and
+independent of arrival order; for a floating VOIDTensor (the reference's own argument type) they
+are fp32 and their last bits depend on the order, as the reference's locked adds do.
 """
 from dataclasses import dataclass
 from typing import Optional
@@ -17,6 +19,7 @@ from typing import Optional
 import torch
 
 from . import _lib, _spmm
+from .format import VOIDTensor
 from .int_quant import Int8VOIDTensor, _resolve_b
 
 
@@ -47,13 +50,13 @@ def compute_stream_k_workload(void_tensor, n_workers: Optional[int] = None,
                            chunk_tiles=target, worker_offsets=woff)
 
 
-def _plan_for(a: Int8VOIDTensor, packed, N: int, workload: StreamKWorkload, per_worker: bool, n_cta: Optional[int]):
+def _plan_for(a, packed, N: int, workload: StreamKWorkload, per_worker: bool, n_cta: Optional[int]):
     sms = _spmm.sm_count(packed.tiles.device)
-    np_ = _spmm.default_panels(packed.nbr, N, sms)
+    np_ = _spmm.default_panels(packed.nbr, N, sms) if _lib.KIND_ELEM_BYTES[packed.kind] == 1 else 1
     if n_cta is None:
         n_cta = sms * 4          # four slim CTAs per SM
     mode = 2 if per_worker else 1
-    key = ("streamk", N, np_, n_cta, mode, workload.chunk_tiles)
+    key = ("streamk", packed.kind, N, np_, n_cta, mode, workload.chunk_tiles)
     cache = getattr(a, "_plan_cache", None)
     if cache is None:
         cache = a._plan_cache = {}
@@ -69,17 +72,20 @@ def void_spmm_stream_k(a: Int8VOIDTensor, b: torch.Tensor, workload: Optional[St
                        activation: int = 0, bias: Optional[torch.Tensor] = None,
                        worker_partials: Optional[torch.Tensor] = None, acc_out: Optional[torch.Tensor] = None,
                        n_cta: Optional[int] = None) -> torch.Tensor:
-    """Load-balanced INT8 SpMM (void/stream_k.py:233-301) with the fused epilogue of void_spmm_int8.
+    """Load-balanced SpMM (void/stream_k.py:233-301): a floating VOIDTensor as in the reference, or an
+    Int8VOIDTensor with the fused epilogue of void_spmm_int8 (``b_scale`` / ``out_dtype`` apply to it).
 
     ``worker_partials`` (int32 [n_segments, 32, N], see the plan's segment list) makes every worker of
     the table a segment of its own and records its partial sum - the check that the sum of the
     partials is the row accumulator.
     """
-    if not isinstance(a, Int8VOIDTensor):
-        raise NotImplementedError("void_spmm_stream_k on B200 takes an Int8VOIDTensor (quantize_void_tensor)")
     assert b.dim() == 2
     assert a.shape[1] == b.shape[0]
     _lib.require_cuda(a.values, b)
+    if isinstance(a, VOIDTensor):
+        return _stream_k_fp(a, b, workload, out, activation, bias, worker_partials, acc_out, n_cta)
+    if not isinstance(a, Int8VOIDTensor):
+        raise TypeError("void_spmm_stream_k takes a VOIDTensor or an Int8VOIDTensor, got %s" % type(a).__name__)
     M, K = a.shape
     N = b.shape[1]
     b_q, scalar, col_scale = _resolve_b(b, b_scale)
@@ -90,20 +96,44 @@ def void_spmm_stream_k(a: Int8VOIDTensor, b: torch.Tensor, workload: Optional[St
         return _spmm.spmm(packed, b_q, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=col_scale, b_scale=scalar,
                           bias=bias, act=activation)
     if workload is None:
-        # the table depends on A's structure only: built once per tensor, then reused
-        workload = getattr(a, "_streamk_workload_cache", None)
-        if workload is None or workload.total_work != a.n_blocks:
-            workload = compute_stream_k_workload(a)
-            a._streamk_workload_cache = workload
+        workload = _cached_workload(a)
     plan = _plan_for(a, packed, N, workload, worker_partials is not None, n_cta)
     return _spmm.spmm(packed, b_q, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=col_scale, b_scale=scalar, bias=bias,
                       act=activation, plan=plan, worker_partials=worker_partials, acc_out=acc_out)
 
 
-def stream_k_plan(a: Int8VOIDTensor, N: int, workload: StreamKWorkload, per_worker: bool = False,
-                  n_cta: Optional[int] = None) -> _spmm.Plan:
-    """The device-built work plan void_spmm_stream_k uses for an N-column product."""
-    return _plan_for(a, a.packed(), N, workload, per_worker, n_cta)
+def _cached_workload(a) -> StreamKWorkload:
+    """The table depends on A's structure only: built once per tensor, then reused."""
+    workload = getattr(a, "_streamk_workload_cache", None)
+    if workload is None or workload.total_work != a.n_blocks:
+        workload = compute_stream_k_workload(a)
+        a._streamk_workload_cache = workload
+    return workload
+
+
+def _stream_k_fp(a: VOIDTensor, b, workload, out, activation, bias, worker_partials, acc_out, n_cta):
+    """void_spmm_stream_k on a floating VOIDTensor (void/stream_k.py:233-301): result in B's dtype."""
+    from . import ops
+    if a.n_blocks == 0:
+        return ops.void_spmm(a, b, out, activation=activation, bias=bias)
+    if workload is None:
+        workload = _cached_workload(a)
+    packed = ops.packed_fp(a, ops.product_kind(a, b))
+    plan = _plan_for(a, packed, b.shape[1], workload, worker_partials is not None, n_cta)
+    return ops.void_spmm(a, b, out, activation=activation, bias=bias, plan=plan, acc_out=acc_out,
+                         worker_partials=worker_partials)
+
+
+def stream_k_plan(a, N: int, workload: StreamKWorkload, per_worker: bool = False, n_cta: Optional[int] = None,
+                  kind: Optional[int] = None) -> _spmm.Plan:
+    """The device-built work plan void_spmm_stream_k uses for an N-column product (``kind``: the
+    product kind of a floating VOIDTensor, fp32 operands by default)."""
+    if isinstance(a, VOIDTensor):
+        from . import ops
+        packed = ops.packed_fp(a, _lib.FP_KIND.get(a.values.dtype, _lib.KIND_TF32) if kind is None else kind)
+    else:
+        packed = a.packed()
+    return _plan_for(a, packed, N, workload, per_worker, n_cta)
 
 
 def analyze_workload_balance(void_tensor) -> dict:
