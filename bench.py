@@ -12,6 +12,9 @@ batch of synthetic input.  Workloads:
                       rank, B replicated by one NCCL broadcast at set-up, no collective in the step
                       (weak scaling: work per GPU is fixed).
   fp8                 same shape, A and B in FP8 E4M3 (per-block / per-column scales), fp32 accumulate.
+  fp32 / fp16         same shape, floating-point void_spmm (fp32 operands multiplied as TF32, or fp16
+                      operands; fp32 accumulate; result in the operands' type).  fp32 is the
+                      configuration of the reference's published SpMM timings (vs_baseline).
   powerlaw            16384 x 16384, Zipf(1.5) tile-row lengths, N = 256, INT8, Stream-K + GELU, bf16 out.
   sharded             65536 x 65536 at 95 %, N = 1024, INT8, ROW_WISE shards over the ranks (strong
                       scaling: the total work is fixed).
@@ -46,12 +49,26 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded", "fp32", "fp16"])
     ap.add_argument("--sparsity", type=float, default=0.9)
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="distinct input copies to rotate over (0 = enough for L2)")
     return ap.parse_args()
+
+
+# The reference's only published timings on this path's shape: fp32 void_spmm, 4096 x 4096, N = 512, on an
+# unnamed "RTX GPU" (its README.md:150-158), milliseconds by block sparsity.
+PUBLISHED_FP32_MS = {0.70: 0.28, 0.80: 0.19, 0.90: 0.12, 0.95: 0.06, 0.98: 0.04}
+
+
+def vs_published(args, world, ms_per_step):
+    """value / published value for the one configuration the reference published (same tiles and
+    operation count on both sides, so the ratio of TFLOP/s is the ratio of times); None otherwise."""
+    if args.workload != "fp32" or world != 1:
+        return None
+    ref_ms = PUBLISHED_FP32_MS.get(round(args.sparsity, 2))
+    return None if ref_ms is None else ref_ms / ms_per_step
 
 
 def measured_peaks():
@@ -163,7 +180,12 @@ def cpu_workload(args, np, torch, vo):
     vals = torch.randn(len(rows), 32, 32, generator=g).numpy()
     b = torch.randn(mask.shape[1] * 32, N, generator=g).numpy()
     shape = (mask.shape[0] * 32, mask.shape[1] * 32)
-    if args.workload == "fp8":
+    if args.workload in ("fp32", "fp16"):
+        np_dt = np.float32 if args.workload == "fp32" else np.float16
+        vals_t, b_t = vals.astype(np_dt), b.astype(np_dt)
+        run = lambda: vo.spmm_fp(vals_t, rows, cols, shape, b_t).astype(np_dt)
+        dtype = "tf32" if args.workload == "fp32" else "f16"
+    elif args.workload == "fp8":
         q, s, _, _ = vo.quantize_fp8_tiles(vals)
         bq, bs, _ = vo.quantize_fp8_cols(b)
         b_deq = vo.fp8_bytes_to_float(bq) * bs[None, :]
@@ -211,6 +233,9 @@ def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
     else:
         make = lambda seed: workloads.headline(args.sparsity, seed=seed, device=dev)
         N, out_dtype, kind = 512, torch.float16, ("f8e4m3" if args.workload == "fp8" else "i8")
+        if args.workload in ("fp32", "fp16"):
+            out_dtype = torch.float32 if args.workload == "fp32" else torch.float16
+            kind = "tf32" if args.workload == "fp32" else "f16"
     # every rank owns different tile rows of the global A (its own seeds); with several ranks the B
     # quantised here is overwritten by rank 0's B in the broadcast that follows
     n_copies = None
@@ -220,14 +245,18 @@ def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
         if kind == "i8":
             a = void.quantize_void_tensor(w.a)
             bq, bs = void.quantize_cols_int8(w.b)
-        else:
+            a.packed()
+        elif kind == "f8e4m3":
             a = void.void_tensor_to_fp8(w.a)
             bq, bs, _ = void.quantize_cols_fp8(w.b)
-        a.packed()
+            a.packed()
+        else:   # floating-point operands: no scales
+            a, bq, bs = w.a.to_dtype(out_dtype), w.b.to(out_dtype), torch.ones(1, device=dev)
         out = torch.empty(w.shape[0], N, dtype=out_dtype, device=dev)
         sets.append([a, bq.contiguous(), bs, out])
         if n_copies is None:
-            per_copy = workloads.algorithmic_bytes(w.nnz, w.shape[0] // 32, w.shape[1], N, w.shape[0], out.element_size())
+            per_copy = workloads.algorithmic_bytes(w.nnz, w.shape[0] // 32, w.shape[1], N, w.shape[0], out.element_size(),
+                                                   bq.element_size())
             n_copies = copies_hint if copies_hint > 0 else max(2, -(-2 * L2_BYTES // per_copy))
         del w
         i += 1
@@ -286,8 +315,10 @@ def main():
             void.void_spmm_stream_k(a, bq, b_scale=bs, out=out, activation=_lib.ACT_GELU)
         elif kind == "i8":
             void.void_spmm_int8(a, bq, bs, out)
-        else:
+        elif kind == "f8e4m3":
             void.void_spmm_fp8(a, bq, out.dtype, b_scale=bs, out=out)
+        else:
+            void.void_spmm(a, bq, out)
 
     # per-step work of this rank
     nnz_local = [s[0].n_blocks for s in sets]
@@ -296,7 +327,8 @@ def main():
     a0 = sets[0][0]
     M_local, K = a0.shape
     bytes_per_step = float(np.mean([workloads.algorithmic_bytes(n, a0.block_grid[0], K, N, M_local,
-                                                                sets[0][3].element_size()) for n in nnz_local]))
+                                                                sets[0][3].element_size(), sets[0][1].element_size())
+                                   for n in nnz_local]))
 
     for i in range(max(args.warmup, 3)):
         step(i)
@@ -366,7 +398,7 @@ def main():
     DEPTH = 3
     slots = []
     for _ in range(DEPTH):
-        h_b = torch.empty(bq_e.shape, dtype=torch.uint8).pin_memory()
+        h_b = torch.empty(bq_e.view(torch.uint8).shape, dtype=torch.uint8).pin_memory()
         h_b.copy_(bq_e.view(torch.uint8).cpu())
         slots.append({"h_b": h_b, "h_s": bs_e.cpu().pin_memory(),
                       "h_c": torch.empty(out_e.shape, dtype=out_e.dtype).pin_memory(),
@@ -380,8 +412,10 @@ def main():
             void.void_spmm_stream_k(a_e, d_b, b_scale=d_s, out=out, activation=_lib.ACT_GELU)
         elif kind == "i8":
             void.void_spmm_int8(a_e, d_b, d_s, out)
-        else:
+        elif kind == "f8e4m3":
             void.void_spmm_fp8(a_e, d_b, out.dtype, b_scale=d_s, out=out)
+        else:
+            void.void_spmm(a_e, d_b, out)
 
     def e2e_step_serial():
         sl = slots[0]
@@ -445,13 +479,14 @@ def main():
         ops_per_byte = ops_per_step_local / bytes_per_step
         clocks = sampler.summary()
         name = info["name"] or ("%s_x%d_rowshards" % (sets[0][0].__class__.__name__, world))
-        if args.workload in ("headline", "fp8"):
+        if args.workload in ("headline", "fp8", "fp32", "fp16"):
             name = "uniform4096_bs%02d_n512%s" % (round(args.sparsity * 100), "" if world == 1 else "_x%d_rowshards" % world)
         elif args.workload == "powerlaw":
             name = "zipf16384_n256_streamk_gelu"
         # ops/byte above (dense 8-bit peak / HBM peak) makes the tensor cores the bound; the 8-bit peak is
         # taken as twice the measured bf16 GEMM rate (the ratio of the nominal dense figures)
-        peak_tops = 2.0 * peaks["bf16_tflops"]
+        # (fp16: the bf16 rate itself; fp32 operands as TF32: half of it)
+        peak_tops = {"tf32": 0.5, "f16": 1.0}.get(kind, 2.0) * peaks["bf16_tflops"]
         tensor_bound = ops_per_byte > peak_tops * 1e12 / (peaks["hbm_gbs"] * 1e9)
         local_tops = ops_per_step_local / (ms_per_step * 1e-3) / 1e12
         roofline = {"bound": "tensor" if tensor_bound else "hbm",
@@ -466,7 +501,8 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": K_steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if args.workload == "sharded" else "weak", "vs_baseline": None,
+            "scaling": "strong" if args.workload == "sharded" else "weak",
+            "vs_baseline": vs_published(args, world, ms_per_step),
             "dtype": kind, "data": "synthetic",
             "config": {"workload": name, "M_per_gpu": M_local, "K": K, "N": N, "tile": 32,
                        "nnz_tiles": nnz_total, "out_dtype": str(sets[0][3].dtype).replace("torch.", ""),

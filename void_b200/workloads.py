@@ -106,10 +106,11 @@ def sharded_int8(M: int = 65536, N: int = 1024, block_sparsity: float = 0.95, se
     return shard, (start, end), int(mask.sum())
 
 
-def algorithmic_bytes(nnz: int, nbr: int, K: int, N: int, M: int, out_bytes: int) -> int:
-    """Bytes one SpMM has to move at least: every stored 8-bit tile with its scale and column index,
-    row_ptr, all of B, B's column scales, and C once."""
-    return nnz * (1024 + 4 + 4) + (nbr + 1) * 4 + K * N + N * 4 + M * N * out_bytes
+def algorithmic_bytes(nnz: int, nbr: int, K: int, N: int, M: int, out_bytes: int, elem_bytes: int = 1) -> int:
+    """Bytes one SpMM has to move at least: every stored tile with its column index (and, for the
+    8-bit kinds, its scale), row_ptr, all of B (with its column scales for the 8-bit kinds), and C once."""
+    scales = 4 if elem_bytes == 1 else 0
+    return nnz * (1024 * elem_bytes + 4 + scales) + (nbr + 1) * 4 + K * N * elem_bytes + N * scales + M * N * out_bytes
 
 
 def spmm_ops(nnz: int, N: int) -> int:
