@@ -231,7 +231,7 @@ typedef struct void_spmm_args {
   /* debugging aid: when not NULL, 64 uint64 nanosecond timestamps per launched CTA      */
   void* trace;
   int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM) */
-  int32_t reserved;
+  int32_t flags;           /* bit 0: do not prefetch the first work item into L2 (measurements)   */
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

@@ -40,7 +40,7 @@ class SpmmArgs(ctypes.Structure):
         ("partials", c_vp), ("partials_bytes", c_i64), ("counters", c_vp), ("worker_partials", c_vp),
         ("status", c_vp),
         ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
-        ("trace", c_vp), ("cta_shape", c_i32), ("reserved", c_i32),
+        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32),
     ]
 
 

@@ -196,7 +196,7 @@ def prepare_b(b: torch.Tensor, elem_bytes: int = 1) -> torch.Tensor:
 def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode: int, col_scale=None,
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
-         grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None) -> torch.Tensor:
+         grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None, flags: int = 0) -> torch.Tensor:
     """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
@@ -245,6 +245,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     a.panels_per_item, a.stages, a.grid, a.tiles_per_stage = panels_per_item, stages, grid, tiles_per_stage
     a.trace = None if trace is None else trace.data_ptr()
     a.cta_shape = cta_shape
+    a.flags = flags
     with torch.cuda.device(dev):
         if es > 1:
             _lib.check(lib.void_spmm_fp(ctypes.byref(a), packed.kind, _lib.stream_ptr(dev)), "void_spmm_fp")

@@ -88,6 +88,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+// Hints to the copy engine: bring a box of a tensor / a linear range into L2.  Nothing waits on them
+// and nothing is written; a box outside the tensor is legal (it reads nothing).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int32_t x, int32_t y, int32_t z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(m), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // Linear bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16).
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(

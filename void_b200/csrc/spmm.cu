@@ -85,7 +85,8 @@ struct SpmmParams {
   const float* tile_scales;
   const int32_t* row_ptr;
   const float* row_scale;
-  int nbr, n_chunks, N, M;
+  int nbr, nbc, n_chunks, N, M;
+  long long nnz;
   const float* col_scale;
   float b_scale;
   const float* bias;
@@ -104,6 +105,7 @@ struct SpmmParams {
   int group;    // tiles per ring stage
   int stages;   // ring depth
   int use3d;    // B panels of a tile fetched by one 3-D TMA
+  int prefetch; // L2 prefetch of the CTA's first work item
   int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
   int n_items;  // without a plan: nbr * n_chunks
   unsigned long long desc_hi_a;  // B panel  (instruction operand A: MN-major, 128B swizzle)
@@ -355,6 +357,44 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
   }
 }
 
+// L2 prefetch of everything the CTA's first work item will stream: its packed tiles and the B panels of
+// their block columns.  Without a work plan the first item follows from the block index alone, so the
+// call sits BEFORE the wait on the previous kernel of the stream and its requests travel while that
+// kernel drains (measured on B200: the wait returns about 1 us after the previous kernel's last CTA
+// has ended, and most CTAs of this kernel are resident well before that).  Run by an epilogue warp,
+// which has nothing else to do until the first accumulator is complete.
+// The index arrays read here may not be final yet (the previous kernel could be the one that writes
+// them): they are read around L1 so that no stale line stays behind, every index is clamped into its
+// array, and the values are used for hints only - a wrong hint costs a little bandwidth, never
+// correctness.  With a plan the first item would have to come from the plan's arrays; measured, a
+// prefetch issued after the wait only competes with the ring's own loads, so there is none.
+template <int ES>
+__device__ __forceinline__ void prefetch_first_item(const SpmmParams& p, const CUtensorMap* tmap, int lane) {
+  if (p.tiles == nullptr || p.nnz <= 0 || p.segs != nullptr) return;
+  const int item = (int)blockIdx.x;
+  if (item >= p.n_items) return;
+  const int row = item / p.n_chunks;
+  const int chunk = item - row * p.n_chunks;
+  long long t0 = __ldcv(p.row_ptr + row);
+  long long t1 = __ldcv(p.row_ptr + row + 1);
+  t0 = t0 < 0 ? 0 : (t0 > p.nnz ? p.nnz : t0);
+  t1 = t1 < t0 ? t0 : (t1 > p.nnz ? p.nnz : t1);
+  if (t1 - t0 > 64) t1 = t0 + 64;   // two rounds of the warp are plenty: later tiles ride on the ring's own run-ahead
+  if (t1 == t0) return;
+  if (lane == 0) bulk_prefetch(p.tiles + (size_t)t0 * (kTileBytes * ES), (uint32_t)(t1 - t0) * (kTileBytes * ES));
+  const int npan = panels_in_chunk(p, chunk);
+  const int n0 = chunk * p.np * kPanelN;
+  for (long long t = t0 + lane; t < t1; t += 32) {
+    int col = __ldcv(p.tile_cols + t);
+    col = col < 0 ? 0 : (col >= p.nbc ? p.nbc - 1 : col);
+    if (p.use3d) {
+      tma_prefetch_3d(tmap, 0, col * kTile, chunk * p.np * ES);
+    } else {
+      for (int q = 0; q < npan * ES; ++q) tma_prefetch_2d(tmap, n0 + q * (kPanelN / ES), col * kTile);
+    }
+  }
+}
+
 template <int KIND>
 __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   if (KIND == VOID_KIND_I8) mma_i8(d, a, b, idesc, acc);
@@ -363,10 +403,14 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, ui
   else mma_f16(d, a, b, idesc, acc);
 }
 
-template <class C>
+template <class C, int ES>
 __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtensorMap* tmap, PipeBars& bars,
                                                uint32_t* tmem_base_s, int* abort_s, int n_acc, uint32_t tmem_cols) {
   const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) stamp(p, 62);
+  // without a plan the first item is known from the block index alone: its lines are requested
+  // while the previous kernel of the stream may still be running
+  if (warp == C::EPI0 && p.prefetch) prefetch_first_item<ES>(p, tmap, threadIdx.x & 31);
   if (threadIdx.x == 0) {
     *abort_s = 0;
     for (int s = 0; s < p.stages; ++s) {
@@ -388,6 +432,7 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
   // this one runs; nothing above touched global memory, everything below may, so wait here until
   // the kernel before this one has completed and its writes are visible.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) stamp(p, 63);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) stamp(p, 0);
   tc_fence_before();
@@ -438,7 +483,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   volatile int* abort_flag = &abort_s;
 
   if (threadIdx.x == 0) last_s = 0;
-  pipeline_setup<C>(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
+  pipeline_setup<C, ES>(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
@@ -569,12 +614,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll
               for (int k = 0; k < 16; ++k) r[k] = 0u;
             }
+            if (epi_tid == 0 && q == 0) stamp(p, 9 + (c >> 4) * 2);
             if (q == npan - 1 && c + 16 >= C::COLS) {  // this warp is done with the accumulator buffer
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
             }
             finish16<KIND>(od, s.row, n, m_first + c, r, rs, cs, bias);
+            if (epi_tid == 0 && q == 0) stamp(p, 10 + (c >> 4) * 2);
           }
           cs = cs_next;
           bias = bias_next;
@@ -702,7 +749,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
   const int n_slots = (int)(kTmemCols / group_cols);   // >= 2: checked at launch
   volatile int* abort_flag = &abort_s;
 
-  pipeline_setup<C>(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
+  pipeline_setup<C, 1>(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
@@ -999,6 +1046,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.row_ptr = a->row_ptr;
   p.row_scale = a->row_scale;
   p.nbr = a->nbr;
+  p.nbc = a->nbc;
+  p.nnz = a->nnz;
   p.n_chunks = n_chunks;
   p.N = a->N;
   p.M = a->M;
@@ -1022,6 +1071,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.stages = stages;
   p.use3d = (a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
+  p.prefetch = (a->flags & 1) ? 0 : 1;
   p.n_items = a->nbr * n_chunks;
 
   // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
