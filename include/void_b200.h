@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define VOID_B200_ABI_VERSION 1
+#define VOID_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define VOID_API __attribute__((visibility("default")))
@@ -232,6 +232,9 @@ typedef struct void_spmm_args {
   void* trace;
   int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM) */
   int32_t flags;           /* bit 0: do not prefetch the first work item into L2 (measurements)   */
+  /* [M] bias added per OUTPUT ROW before the activation, or NULL: the linear-layer form
+   * act(W x + b[:, None]) of void_spmm_activation_row_bias_kernel, void/fusion.py:201-304 */
+  const float* row_bias;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

@@ -251,6 +251,25 @@ def gelu_tanh_sigmoid(x):
     return (x * np.float32(0.5) * (np.float32(1.0) + t)).astype(np.float32)
 
 
+def silu(x):
+    """_silu of void/fusion.py:53-56: x * sigmoid(x) in fp32."""
+    x = np.asarray(x, dtype=np.float32)
+    return (x * (np.float32(1.0) / (np.float32(1.0) + np.exp(-x)))).astype(np.float32)
+
+
+def sparse_mlp(w1, w2, x, bias1=None, bias2=None, act=gelu_tanh_sigmoid):
+    """fused_sparse_mlp, void/fusion.py:557-602: y = (W2 @ act(W1 @ x^T + b1[:, None]) + b2[:, None])^T with the
+    row-bias kernel of :201-304 for both layers.  w1 / w2 = (values, block_rows, block_cols, shape); x [batch, in]."""
+    h = spmm_fp(*w1, np.ascontiguousarray(np.asarray(x, dtype=np.float32).T))
+    if bias1 is not None:
+        h = h + np.asarray(bias1, dtype=np.float32)[:, None]
+    h = act(h)
+    y = spmm_fp(*w2, h)
+    if bias2 is not None:
+        y = y + np.asarray(bias2, dtype=np.float32)[:, None]
+    return np.ascontiguousarray(y.T)
+
+
 # ----------------------------------------------------------------------------- Stream-K
 def stream_k_workload(row_ptr, n_blocks, n_workers=None, max_work_per_worker=16):
     """The worker table of compute_stream_k_workload, void/stream_k.py:55-110.

@@ -37,7 +37,8 @@ import triton  # noqa: E402
 
 import void  # noqa: E402
 from void.fp8 import FP8Config, quantize_to_fp8, void_spmm_fp8_kernel, void_tensor_to_fp8, compute_amax  # noqa: E402
-from void.fusion import void_spmm_activation_kernel  # noqa: E402
+from void.fusion import (void_spmm_activation_kernel, void_spmm_activation_row_bias_kernel,  # noqa: E402
+                         get_activation_code)
 from void.int_quant import (IntQuantConfig, ScaleMode, quantize_tensor, quantize_void_tensor,  # noqa: E402
                             void_spmm_int8)
 from void.ops import get_triton_dtype  # noqa: E402
@@ -121,6 +122,26 @@ def ref_gelu_spmm(vt, b, bias):
         M, N, K, vt.n_blocks, nbr, b.stride(0), b.stride(1), out.stride(0), out.stride(1), has_bias,
         TILE_M=vt.tile_size[0], TILE_K=vt.tile_size[1], TILE_N=TILE_N, ACTIVATION=2,
         OUTPUT_DTYPE=get_triton_dtype(b.dtype))
+    return out
+
+
+def ref_row_bias_spmm(vt, b, bias, activation):
+    """_void_spmm_activation_row_bias without its CUDA assert, void/fusion.py:352-377."""
+    M, K = vt.shape
+    N = b.shape[1]
+    b = b.contiguous()
+    out = torch.zeros(M, N, dtype=b.dtype)
+    row_ptr, block_indices = vt.get_row_block_info()
+    nbr = vt.block_grid[0]
+    TILE_N = void.compute_optimal_tile_n(N)
+    has_bias = 1 if bias is not None else 0
+    bias_t = bias.contiguous() if bias is not None else torch.empty(1)
+    grid = (nbr, triton.cdiv(N, TILE_N))
+    void_spmm_activation_row_bias_kernel[grid](
+        vt.values, vt.block_rows, vt.block_cols, row_ptr, block_indices, b, bias_t, out,
+        M, N, K, vt.n_blocks, nbr, b.stride(0), b.stride(1), out.stride(0), out.stride(1), has_bias,
+        TILE_M=vt.tile_size[0], TILE_K=vt.tile_size[1], TILE_N=TILE_N,
+        ACTIVATION=get_activation_code(activation), OUTPUT_DTYPE=get_triton_dtype(b.dtype))
     return out
 
 
@@ -278,7 +299,17 @@ def main():
     x = torch.from_numpy(rng.standard_normal(270).astype(np.float32))
     wl = compute_stream_k_workload(vt, n_workers=12, max_work_per_worker=2)
     assert wl.worker_needs_atomic.any()
-    save("fp_small.npz", **coo_inputs(m), b=b.numpy(), bias=bias.numpy(), x=x.numpy(),
+    # two-layer MLP y = W2 @ gelu(W1 @ x^T + b1) + b2 (fused_sparse_mlp, void/fusion.py:557-602) on x = b^T
+    m2 = block_sparse_csr(rng, 3, 7, 0.6, M=70, K=200)
+    w2 = void.csr_to_void(m2, tile_size=32)
+    bias1 = torch.from_numpy(rng.standard_normal(200).astype(np.float32))
+    bias2 = torch.from_numpy(rng.standard_normal(70).astype(np.float32))
+    hidden = ref_row_bias_spmm(vt, b, bias1, "gelu")
+    mlp = ref_row_bias_spmm(w2, hidden, bias2, "none").T.contiguous()
+    w2c = m2.tocoo()
+    save("fp_small.npz", **coo_inputs(m), w2_row=w2c.row.astype(np.int32), w2_col=w2c.col.astype(np.int32),
+         w2_data=w2c.data.astype(np.float32), bias1=bias1.numpy(), bias2=bias2.numpy(),
+         rowbias_gelu=hidden.numpy(), rowbias_silu=ref_row_bias_spmm(vt, b, bias1, "silu").numpy(), mlp=mlp.numpy(), b=b.numpy(), bias=bias.numpy(), x=x.numpy(),
          block_rows=vt.block_rows.numpy(), block_cols=vt.block_cols.numpy(),
          c_fp32=void.void_spmm(vt, b).numpy(),
          c_f16=void.void_spmm(vt.half(), b.half()).float().numpy(),

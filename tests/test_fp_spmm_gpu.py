@@ -72,6 +72,40 @@ def test_fp_small_all_entry_points_vs_reference_output():
     void.check_device_status()
 
 
+def test_row_bias_mlp_and_linear_module_vs_reference_output():
+    import scipy.sparse as sp
+    g = load_golden("fp_small.npz")
+    w1 = void.csr_to_void(coo_to_csr(g), tile_size=32, device="cuda")
+    w2 = void.csr_to_void(sp.csr_matrix((g["w2_data"], (g["w2_row"], g["w2_col"])), shape=(70, 200)), tile_size=32,
+                          device="cuda")
+    b = torch.from_numpy(g["b"]).cuda()
+    b1, b2 = torch.from_numpy(g["bias1"]).cuda(), torch.from_numpy(g["bias2"]).cuda()
+    from void_b200.fusion import _void_spmm_activation_row_bias
+    h = _void_spmm_activation_row_bias(w1, b, b1, None, "gelu")
+    assert rel_err(_np(h), g["rowbias_gelu"]) < TF32_BAR
+    assert rel_err(_np(_void_spmm_activation_row_bias(w1, b, b1, None, "silu")), g["rowbias_silu"]) < TF32_BAR
+    x = b.T.contiguous()                                                    # [batch 80, in 270]
+    y = void.fused_sparse_mlp(x, w1, w2, "gelu", b1, b2)
+    assert y.shape == (80, 70) and rel_err(_np(y), g["mlp"]) < 2 * TF32_BAR  # two TF32 products in a row
+    y3 = void.fused_sparse_mlp(x.reshape(4, 20, 270), w1, w2, "gelu", b1, b2)
+    assert y3.shape == (4, 20, 70) and torch.equal(y3.reshape(80, 70), y)
+    assert torch.equal(void.create_sparse_mlp(w1, w2, "gelu", b1, b2)(x), y)
+    assert torch.equal(void.create_fused_spmm_gelu(w1)(b), void.void_spmm_gelu(w1, b))
+    lin = void.FusedSparseLinear(270, 200, w1, activation="gelu", bias=True)
+    with torch.no_grad():
+        lin.bias.copy_(b1)
+    assert torch.equal(lin(x), h.T) and "in_features=270" in repr(lin)
+    with pytest.raises(AssertionError):
+        _void_spmm_activation_row_bias(w1, b, b2, None, "gelu")            # wrong bias length
+    # the same epilogue on the quantized kernel (extension): bias per row after dequantisation
+    q = void.quantize_void_tensor(w1)
+    bq, bs = void.quantize_cols_int8(b)
+    pre = void.void_spmm_int8(q, bq, bs)
+    got = _void_spmm_activation_row_bias(q, bq, b1, None, "relu", b_scale=bs)
+    assert torch.allclose(got, torch.relu(pre + b1[:, None]), rtol=1e-6, atol=1e-6)
+    void.check_device_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("n", [32, 96, 200, 512])
 def test_fp_spmm_shapes_and_dtypes(dtype, n):

@@ -82,6 +82,13 @@ def test_fp_spmm_c1_and_small():
     assert rel_err(vo.spmm_fp(*args, g["x"][:, None])[:, 0], g["y_spmv"]) < 1e-6
     assert rel_err(vo.gelu_tanh_sigmoid(c), g["gelu"]) < 1e-6
     assert rel_err(vo.gelu_tanh_sigmoid(c + g["bias"][None, :]), g["gelu_bias"]) < 1e-6
+    # bias per output row (the linear-layer kernel, void/fusion.py:201-304) and the two-layer MLP built on it
+    assert rel_err(vo.gelu_tanh_sigmoid(c + g["bias1"][:, None]), g["rowbias_gelu"]) < 1e-6
+    assert rel_err(vo.silu(c + g["bias1"][:, None]), g["rowbias_silu"]) < 1e-6
+    import scipy.sparse as sp
+    f2 = vo.csr_to_void_fields(sp.csr_matrix((g["w2_data"], (g["w2_row"], g["w2_col"])), shape=(70, 200)))
+    w2 = (f2["values"], f2["block_rows"], f2["block_cols"], f2["shape"])
+    assert rel_err(vo.sparse_mlp(args, w2, g["b"].T, g["bias1"], g["bias2"]), g["mlp"]) < 1e-6
     # fp16 tiles and fp16 B: products in fp32, result rounded to fp16 once
     c16 = vo.spmm_fp(f["values"].astype(np.float16), *args[1:], g["b"].astype(np.float16))
     assert rel_err(c16.astype(np.float16).astype(np.float32), g["c_f16"]) < 1e-3

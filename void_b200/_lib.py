@@ -14,6 +14,7 @@ from . import build as _build
 _LOCK = threading.Lock()
 _LIB = None
 
+ABI_VERSION = 2
 c_i32, c_i64, c_f32, c_vp, c_sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 
 # enums of include/void_b200.h
@@ -40,7 +41,7 @@ class SpmmArgs(ctypes.Structure):
         ("partials", c_vp), ("partials_bytes", c_i64), ("counters", c_vp), ("worker_partials", c_vp),
         ("status", c_vp),
         ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
-        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32),
+        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp),
     ]
 
 
@@ -100,7 +101,7 @@ def load():
             fn = getattr(lib, name)  # AttributeError if the library does not export it
             fn.restype = res
             fn.argtypes = args
-        if lib.void_b200_abi_version() != 1:
+        if lib.void_b200_abi_version() != ABI_VERSION:
             raise VoidB200Error("void_b200: ABI version mismatch, rebuild with python -m void_b200.build --force")
         _LIB = lib
     return _LIB

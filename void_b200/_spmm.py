@@ -196,7 +196,8 @@ def prepare_b(b: torch.Tensor, elem_bytes: int = 1) -> torch.Tensor:
 def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode: int, col_scale=None,
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
-         grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None, flags: int = 0) -> torch.Tensor:
+         grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None, flags: int = 0,
+         row_bias=None) -> torch.Tensor:
     """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
@@ -229,6 +230,12 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
         bias = bias.to(device=dev, dtype=torch.float32).contiguous()
         keep.append(bias)
         a.bias = bias.data_ptr()
+    if row_bias is not None:
+        row_bias = row_bias.to(device=dev, dtype=torch.float32).contiguous()
+        if row_bias.numel() != M:
+            raise _lib.VoidB200Error("row bias must have %d elements, got %d" % (M, row_bias.numel()))
+        keep.append(row_bias)
+        a.row_bias = row_bias.data_ptr()
     a.out, a.ldc, a.M = out.data_ptr(), out.stride(0), M
     a.out_dtype = _lib.OUT_DTYPE_CODE[out.dtype]
     a.act = act

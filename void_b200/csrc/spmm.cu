@@ -90,6 +90,7 @@ struct SpmmParams {
   const float* col_scale;
   float b_scale;
   const float* bias;
+  const float* row_bias;
   void* out;
   long long ldc;
   int out_dtype, act;
@@ -171,11 +172,12 @@ struct OutDesc {
   void* out;
   long long ldc;
   void* acc_out;
+  const float* row_bias;  // [M] added per output row before the activation (linear-layer bias), or null
   int M, N, dtype, act;
 };
 __device__ __forceinline__ OutDesc out_desc(const SpmmParams& p) {
   OutDesc o;
-  o.out = p.out; o.ldc = p.ldc; o.acc_out = p.acc_out; o.M = p.M; o.N = p.N; o.dtype = p.out_dtype; o.act = p.act;
+  o.out = p.out; o.ldc = p.ldc; o.acc_out = p.acc_out; o.row_bias = p.row_bias; o.M = p.M; o.N = p.N; o.dtype = p.out_dtype; o.act = p.act;
   return o;
 }
 
@@ -183,6 +185,11 @@ __device__ __forceinline__ OutDesc out_desc(const SpmmParams& p) {
 __device__ __forceinline__ void store8(const OutDesc& o, int row, int n, int m0, float (&v)[8]) {
   const int r0 = row * kTile + m0;
   const int rows = o.M - r0;  // rows left below r0
+  if (o.row_bias != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < rows) v[k] += __ldg(o.row_bias + r0 + k);
+  }
   switch (o.act) {
     case VOID_ACT_RELU:
 #pragma unroll
@@ -248,6 +255,13 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
     const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
     v[k] = (x * row_scale) * cs + bias;
   }
+  const int r0 = row * kTile + m0;
+  const int rows = o.M - r0;
+  if (o.row_bias != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+      if (k < rows) v[k] += __ldg(o.row_bias + r0 + k);
+  }
   if (o.act != VOID_ACT_NONE) {
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
@@ -256,8 +270,6 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
       else v[k] = v[k] * fast_sigmoid(v[k]);
     }
   }
-  const int r0 = row * kTile + m0;
-  const int rows = o.M - r0;
   const size_t first = (size_t)r0 * o.ldc + n;
   if (o.dtype == VOID_OUT_F16) {
     __half* dst = reinterpret_cast<__half*>(o.out) + first;
@@ -1054,6 +1066,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.col_scale = a->col_scale;
   p.b_scale = a->b_scale;
   p.bias = a->bias;
+  p.row_bias = a->row_bias;
   p.out = a->out;
   p.ldc = a->ldc;
   p.out_dtype = a->out_dtype;

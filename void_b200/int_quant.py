@@ -253,7 +253,7 @@ def _resolve_b(b: torch.Tensor, b_scale):
 def void_spmm_int8(a: Int8VOIDTensor, b: torch.Tensor, b_scale: Union[None, float, torch.Tensor] = None,
                    out: Optional[torch.Tensor] = None, *, out_dtype: Optional[torch.dtype] = None,
                    exact_scales: bool = False, acc_out: Optional[torch.Tensor] = None, activation: int = 0,
-                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   bias: Optional[torch.Tensor] = None, row_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """INT8 sparse-dense product C = dequant(A_q . B_q) (void/int_quant.py:543-612).
 
     a: Int8VOIDTensor [M, K];  b: int8 [K, N] (or floating point, then quantised per tensor);
@@ -272,7 +272,7 @@ def void_spmm_int8(a: Int8VOIDTensor, b: torch.Tensor, b_scale: Union[None, floa
     # every element of out is written by the kernel (zeros for empty tile rows), so the
     # reference's torch.zeros / out.zero_() (:580-583) has no counterpart here
     return _spmm.spmm(packed, b_q, out, scale_mode=mode, col_scale=col_scale, b_scale=scalar, bias=bias,
-                      act=activation, acc_out=acc_out)
+                      act=activation, acc_out=acc_out, row_bias=row_bias)
 
 
 def get_quantization_error(original: torch.Tensor, config: IntQuantConfig) -> dict:

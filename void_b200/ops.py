@@ -49,12 +49,13 @@ def packed_fp(a: VOIDTensor, kind: int) -> _spmm.PackedTiles:
 
 
 def void_spmm(a: VOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, activation: int = 0,
-              bias: Optional[torch.Tensor] = None, plan=None, acc_out: Optional[torch.Tensor] = None,
-              worker_partials: Optional[torch.Tensor] = None) -> torch.Tensor:
+              bias: Optional[torch.Tensor] = None, row_bias: Optional[torch.Tensor] = None, plan=None,
+              acc_out: Optional[torch.Tensor] = None, worker_partials: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B (void/ops.py:148-217); ``out`` defaults to a new [M, N] tensor of B's dtype.
 
     Keyword extensions: ``activation`` (code of get_activation_code: none, relu, gelu, silu) and a
-    column ``bias`` fused into the epilogue; ``plan`` (a work plan of stream_k.stream_k_plan).
+    column ``bias`` [N] or a ``row_bias`` [M] fused into the epilogue; ``plan`` (a work plan of
+    stream_k.stream_k_plan).
     """
     assert b.dim() == 2
     assert a.shape[1] == b.shape[0], f"Dimension mismatch: A is {a.shape}, B is {tuple(b.shape)}"
@@ -70,7 +71,7 @@ def void_spmm(a: VOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     if b.dtype != _KIND_DTYPE[kind]:
         b = b.to(_KIND_DTYPE[kind])
     return _spmm.spmm(packed, b, out, scale_mode=_lib.SCALE_ROW_MEAN, use_row_scale=False, bias=bias, act=activation,
-                      plan=plan, acc_out=acc_out, worker_partials=worker_partials)
+                      row_bias=row_bias, plan=plan, acc_out=acc_out, worker_partials=worker_partials)
 
 
 def void_spmv(a: VOIDTensor, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
