@@ -80,6 +80,43 @@ VOID_API int void_build_tile_index(const int32_t* block_rows, const int32_t* blo
                           void* ws, size_t ws_bytes, void_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Format construction on the device.  Replaces the host-side work of dense_to_void,
+ * void/format.py:352-446 (tile norms with torch ops, Morton codes and their sort in numpy
+ * :413-424) and of csr_to_void, :248-349 (numpy throughout, one Python iteration per nonzero
+ * :321-327).  Tiles are 32x32.  The kept tiles are ranked by a bitmap over Morton-code space
+ * (morton(r, c) = bits of r on even positions, bits of c on odd ones, :41-51): rank order is
+ * ascending Morton order, so nothing is sorted.
+ *
+ *   ws = caller workspace of void_format_ws_bytes(nbr, nbc) bytes (0: grid too large, more than
+ *        16384 tiles along a side), shared by the calls of one conversion.
+ *   1. void_dense_mark: a tile is kept when the sum of |x| over it exceeds threshold (:391-394);
+ *      elem = VOID_ELEM_*; or void_csr_mark: a tile is kept when the CSR matrix stores an entry
+ *      in it, zero or not (:287-296).  counts[2] (device, int64) receives the number of kept
+ *      tiles and, for the dense form, the number of nonzero elements (nnz_original, :429).
+ *   2. the caller reads counts[0], allocates, and calls void_morton_emit: block_rows,
+ *      block_cols, morton_codes [n_blocks] in ascending Morton order.
+ *   3. void_dense_gather copies the kept tiles (zero padding outside the matrix, :374-378);
+ *      void_csr_scatter zero-fills values [n_blocks, 32, 32] and places every stored entry
+ *      (entries with equal coordinates race; the reference keeps the later one).
+ * ------------------------------------------------------------------------------------- */
+enum { VOID_ELEM_F32 = 0, VOID_ELEM_F16 = 1, VOID_ELEM_BF16 = 2 };
+VOID_API size_t void_format_ws_bytes(int32_t nbr, int32_t nbc);
+VOID_API int void_dense_mark(const void* matrix, int32_t elem, int64_t ld, int32_t M, int32_t N,
+                             float threshold, void* ws, size_t ws_bytes, int64_t* counts,
+                             void_stream_t stream);
+VOID_API int void_csr_mark(const int32_t* crow, const int32_t* col, int32_t M, int32_t N, void* ws,
+                           size_t ws_bytes, int64_t* counts, void_stream_t stream);
+VOID_API int void_morton_emit(const void* ws, int32_t nbr, int32_t nbc, int64_t n_blocks,
+                              int32_t* block_rows, int32_t* block_cols, int64_t* morton_codes,
+                              void_stream_t stream);
+VOID_API int void_dense_gather(const void* matrix, int32_t elem, int64_t ld, int32_t M, int32_t N,
+                               const int32_t* block_rows, const int32_t* block_cols,
+                               int64_t n_blocks, void* values, void_stream_t stream);
+VOID_API int void_csr_scatter(const int32_t* crow, const int32_t* col, const float* data, int32_t M,
+                              int32_t N, const void* ws, int64_t n_blocks, float* values,
+                              void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Pack.  Gathers the Morton-ordered 8-bit tiles (Int8VOIDTensor.values,
  * void/int_quant.py:116, or FP8VOIDTensor.values_fp8, void/fp8.py:445) into tile-row-major
  * order through block_indices and rewrites each 32x32 tile into 8x16-byte core matrices.

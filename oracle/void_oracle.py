@@ -64,6 +64,29 @@ def csr_to_void_fields(matrix, tile_size=TILE):
     }
 
 
+def dense_to_void_fields(matrix, threshold=0.0, tile_size=TILE):
+    """dense_to_void, void/format.py:352-446: zero-pad to whole tiles (:374-378), keep the tiles whose sum of
+    |x| exceeds the threshold (:391-394), order them by Morton code (:413-424); nnz_original counts the
+    nonzero elements of the unpadded matrix (:429)."""
+    a = np.asarray(matrix)
+    M, N = a.shape
+    nbr, nbc = (M + tile_size - 1) // tile_size, (N + tile_size - 1) // tile_size
+    padded = np.zeros((nbr * tile_size, nbc * tile_size), dtype=a.dtype)
+    padded[:M, :N] = a
+    tiles = padded.reshape(nbr, tile_size, nbc, tile_size).transpose(0, 2, 1, 3)
+    norms = np.abs(tiles).sum(axis=(2, 3))
+    rows, cols = np.nonzero(norms > threshold)
+    codes = morton_encode_batch(rows, cols)
+    order = np.argsort(codes)
+    n = len(rows)
+    return {
+        "values": tiles[rows[order], cols[order]] if n else np.zeros((0, tile_size, tile_size), a.dtype),
+        "block_rows": rows[order].astype(np.int32), "block_cols": cols[order].astype(np.int32),
+        "morton_codes": codes[order].astype(np.int64), "shape": (M, N), "n_blocks": n,
+        "nnz_original": int(np.count_nonzero(a)), "density": (n / (nbr * nbc)) if n else 0.0,
+    }
+
+
 def row_block_info(block_rows, block_cols, nbr, nbc):
     """row_ptr and block_indices of VOIDTensor.get_row_block_info, void/format.py:218-231."""
     block_rows = np.asarray(block_rows, dtype=np.int64)

@@ -20,6 +20,8 @@ Fixtures (all .npz, inputs included so that the tests do not depend on RNG stabi
   fp_small.npz       floating-point void_spmm (fp32 and fp16), void_spmv, fused GELU and the Stream-K
                      kernel on a ragged matrix with empty tile rows
 
+  dense_small.npz    dense_to_void with and without a norm threshold on a ragged matrix
+
 A fixture whose arrays come out identical to the file already present is left untouched.
 """
 import os
@@ -317,6 +319,22 @@ def main():
          gelu=ref_gelu_spmm(vt, b, None).numpy(), gelu_bias=ref_gelu_spmm(vt, b, bias).numpy(),
          stream_k=ref_stream_k(vt, b, wl).numpy(),
          stream_k_meta=np.asarray([wl.n_workers, 12, 2], dtype=np.int64))
+
+    # ---------------------------------------------------------------- dense_small
+    rng = np.random.default_rng(31)
+    dense = block_sparse_csr(rng, 5, 7, 0.5, M=150, K=210, empty_rows=(3,)).toarray()
+    dense[64:96, 0:32] = 0.01 * rng.standard_normal((32, 32)).astype(np.float32)   # a tile with a small L1 norm
+    dense[10, 200] = 3.0                                                            # a single entry in an edge tile
+    out = {"matrix": dense}
+    for tag, thr in (("t0", 0.0), ("t10", 10.0)):
+        vt = void.dense_to_void(torch.from_numpy(dense), tile_size=32, threshold=thr)
+        f = void_fields(vt, tag + "_")
+        del f[tag + "_row_ptr"], f[tag + "_block_indices"]
+        out.update(f)
+        out[tag + "_threshold"] = np.asarray([thr], dtype=np.float32)
+    empty = void.dense_to_void(torch.zeros(40, 50), tile_size=32)
+    out["empty_meta"] = np.asarray([empty.n_blocks, empty.nnz_original], dtype=np.int64)
+    save("dense_small.npz", **out)
 
 
 if __name__ == "__main__":

@@ -29,6 +29,57 @@ def test_csr_to_void_and_tile_index(name):
     assert a.get_row_block_info()[0] is row_ptr  # cached
 
 
+def test_csr_to_void_device_builder_equals_host_builder():
+    import scipy.sparse as sp
+    rs = np.random.RandomState(3)
+    m = sp.random(1500, 2100, density=0.002, format="csr", dtype=np.float32, random_state=rs)
+    m.data[::7] = 0.0                                           # stored zeros still activate their tiles
+    dev = void.csr_to_void(m, tile_size=32, device="cuda")     # built by the CUDA library
+    host = void.csr_to_void(m, tile_size=32, device="cpu")     # numpy restatement of the reference's loop
+    f = vo.csr_to_void_fields(m)
+    assert dev.n_blocks == host.n_blocks == f["n_blocks"] and dev.nnz_original == m.nnz and dev.density == host.density
+    for k in ("values", "block_rows", "block_cols", "morton_codes"):
+        assert torch.equal(getattr(dev, k).cpu(), getattr(host, k)), k
+        assert np.array_equal(getattr(dev, k).cpu().numpy(), f[k]), k
+    assert void.csr_to_void(m, device="cuda", dtype=torch.float16).values.dtype == torch.float16
+
+
+def test_dense_to_void_vs_reference_output():
+    g = load_golden("dense_small.npz")
+    a = torch.from_numpy(g["matrix"]).cuda()
+    for tag in ("t0", "t10"):
+        v = void.dense_to_void(a, tile_size=32, threshold=float(g[tag + "_threshold"][0]))
+        assert v.n_blocks == int(g[tag + "_meta"][0]) and v.nnz_original == int(g[tag + "_meta"][1])
+        assert v.density == float(g[tag + "_density"][0]) and v.shape == (150, 210) and v.dtype == torch.float32
+        for k in ("values", "block_rows", "block_cols", "morton_codes"):
+            got = getattr(v, k).cpu().numpy()
+            assert np.array_equal(got, g[tag + "_" + k]) and got.dtype == g[tag + "_" + k].dtype, (tag, k)
+    e = void.dense_to_void(torch.zeros(40, 50, device="cuda"))
+    assert [e.n_blocks, e.nnz_original] == g["empty_meta"].tolist() and e.density == 0.0 and e.values.shape == (0, 32, 32)
+    assert torch.equal(void.dense_to_void(a).to_dense(), a)                          # round trip
+    with pytest.raises(void.VoidB200Error):
+        void.dense_to_void(a.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_dense_to_void_large_and_strided(dtype):
+    gen = torch.Generator().manual_seed(4)
+    keep = (torch.rand(70, 90, generator=gen) < 0.15).repeat_interleave(32, 0).repeat_interleave(32, 1)
+    full = (torch.randn(70 * 32, 90 * 32, generator=gen) * keep)[:2231, :2870].to(dtype)
+    wide = torch.zeros(2231, 3000, dtype=dtype)
+    wide[:, :2870] = full
+    v = void.dense_to_void(wide.cuda()[:, :2870])                                    # row pitch larger than N
+    f = vo.dense_to_void_fields(full.float().numpy())
+    assert v.n_blocks == f["n_blocks"] and v.nnz_original == f["nnz_original"] and v.dtype == dtype
+    assert np.array_equal(v.block_rows.cpu().numpy(), f["block_rows"])
+    assert np.array_equal(v.block_cols.cpu().numpy(), f["block_cols"])
+    assert np.array_equal(v.morton_codes.cpu().numpy(), f["morton_codes"])
+    assert np.array_equal(v.values.float().cpu().numpy(), f["values"])
+    b = torch.randn(2870, 64, generator=gen).to(dtype).cuda()
+    ref = full.float().cuda() @ b.float()
+    assert (void.void_spmm(v, b).float() - ref).abs().max() <= 4e-3 * ref.abs().max()   # TF32 / 16-bit output rounding
+
+
 def test_tile_index_large_random_grid():
     rng = np.random.default_rng(3)
     mask = rng.random((517, 1033)) > 0.93

@@ -30,6 +30,19 @@ def test_csr_to_void_fields(name):
     assert np.array_equal(bidx, g["block_indices"]) and bidx.dtype == np.int32
 
 
+def test_dense_to_void_fields():
+    g = load_golden("dense_small.npz")
+    for tag in ("t0", "t10"):
+        f = vo.dense_to_void_fields(g["matrix"], float(g[tag + "_threshold"][0]))
+        assert f["n_blocks"] == int(g[tag + "_meta"][0]) and f["nnz_original"] == int(g[tag + "_meta"][1])
+        assert f["density"] == float(g[tag + "_density"][0])
+        for k in ("values", "block_rows", "block_cols", "morton_codes"):
+            assert np.array_equal(f[k], g[tag + "_" + k]) and f[k].dtype == g[tag + "_" + k].dtype, (tag, k)
+    assert int(g["t10_meta"][0]) < int(g["t0_meta"][0])            # the threshold drops the faint tiles
+    e = vo.dense_to_void_fields(np.zeros((40, 50), np.float32))
+    assert [e["n_blocks"], e["nnz_original"]] == g["empty_meta"].tolist() and e["density"] == 0.0
+
+
 def test_c1_is_fully_dense_in_blocks():
     g = load_golden("c1_plumbing.npz")
     assert int(g["meta"][0]) == 256  # density 0.1 fills every 32x32 tile of the 16x16 block grid

@@ -7,7 +7,7 @@ void_spmm_stream_k, shard_void_tensor / distributed_void_spmm.  All arithmetic r
 hand-written CUDA behind a C ABI (include/void_b200.h); there is no Triton, no dispatch layer and
 no CPU fallback.
 """
-from .format import (VOIDTensor, csr_to_void, morton_encode, morton_decode, morton_encode_batch,
+from .format import (VOIDTensor, csr_to_void, dense_to_void, morton_encode, morton_decode, morton_encode_batch,
                      void_from_block_mask, MIN_TENSOR_CORE_TILE)
 from .int_quant import (IntFormat, ScaleMode, IntQuantConfig, QuantizationParams, Int8VOIDTensor, quantize_tensor,
                         dequantize_tensor, quantize_void_tensor, dequantize_void_tensor, void_spmm_int8,

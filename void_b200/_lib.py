@@ -26,6 +26,7 @@ ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 SCALE_ROW_MEAN, SCALE_PER_TILE = 0, 1
 
 OUT_DTYPE_CODE = {torch.float32: OUT_F32, torch.float16: OUT_F16, torch.bfloat16: OUT_BF16}
+ELEM_CODE = OUT_DTYPE_CODE   # VOID_ELEM_* uses the same numbering
 
 
 class SpmmArgs(ctypes.Structure):
@@ -51,6 +52,12 @@ _PROTOTYPES = {
     "void_device_sm_count": (ctypes.c_int, []),
     "void_tile_index_ws_bytes": (c_sz, [c_i32, c_i32]),
     "void_build_tile_index": (ctypes.c_int, [c_vp, c_vp, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "void_format_ws_bytes": (c_sz, [c_i32, c_i32]),
+    "void_dense_mark": (ctypes.c_int, [c_vp, c_i32, c_i64, c_i32, c_i32, c_f32, c_vp, c_sz, c_vp, c_vp]),
+    "void_csr_mark": (ctypes.c_int, [c_vp, c_vp, c_i32, c_i32, c_vp, c_sz, c_vp, c_vp]),
+    "void_morton_emit": (ctypes.c_int, [c_vp, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "void_dense_gather": (ctypes.c_int, [c_vp, c_i32, c_i64, c_i32, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "void_csr_scatter": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp]),
     "void_pack_tiles": (ctypes.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "void_pack_tiles_fp": (ctypes.c_int, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_i8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp]),

@@ -1,9 +1,10 @@
 """VOIDTensor format: block-sparse matrices stored as Morton-ordered dense 32x32 tiles.
 
 Mirrors the public surface of void/format.py (VOIDTensor :54-80, morton_encode :15-25,
-morton_encode_batch :41-51, csr_to_void :248-349, get_row_block_info :201-237) so that code
-written against the reference imports unchanged.  The tile index is built by the CUDA library
-(void_build_tile_index); there is no CPU compute path.
+morton_encode_batch :41-51, csr_to_void :248-349, dense_to_void :352-446, get_row_block_info
+:201-237) so that code written against the reference imports unchanged.  The tile index and, for
+device="cuda", the format itself (kept tiles, Morton order, tile values) are built by the CUDA
+library; there is no CPU compute path.
 """
 import warnings
 from dataclasses import dataclass
@@ -165,16 +166,97 @@ class VOIDTensor:
                 f"overhead={self.overhead_ratio:.2f}x, dtype={self.dtype})")
 
 
+def _build_on_device(mark, fill, M: int, N: int, dev, value_dtype: torch.dtype):
+    """Shared tail of the device builders: mark kept tiles, read their count, emit the Morton-ordered
+    index and fill the tile values.  Returns (values, block_rows, block_cols, morton_codes, n_blocks, nnz)."""
+    lib = _lib.load()
+    nbr, nbc = (M + 31) // 32, (N + 31) // 32
+    with torch.cuda.device(dev):
+        ws_bytes = lib.void_format_ws_bytes(nbr, nbc)
+        if ws_bytes == 0:
+            raise _lib.VoidB200Error("block grid %d x %d is too large for the device format builder" % (nbr, nbc))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        counts = torch.zeros(2, dtype=torch.int64, device=dev)
+        mark(lib, ws, ws_bytes, counts)
+        n_blocks, nnz = (int(v) for v in counts.tolist())          # the one synchronisation, like .nonzero()
+        values = torch.empty(n_blocks, 32, 32, dtype=value_dtype, device=dev)
+        block_rows = torch.empty(n_blocks, dtype=torch.int32, device=dev)
+        block_cols = torch.empty(n_blocks, dtype=torch.int32, device=dev)
+        codes = torch.empty(n_blocks, dtype=torch.int64, device=dev)
+        _lib.check(lib.void_morton_emit(_lib.ptr(ws), nbr, nbc, n_blocks, _lib.ptr(block_rows), _lib.ptr(block_cols),
+                                        _lib.ptr(codes), _lib.stream_ptr(dev)), "void_morton_emit")
+        fill(lib, ws, n_blocks, block_rows, block_cols, values)
+    return values, block_rows, block_cols, codes, n_blocks, nnz, nbr * nbc
+
+
+def dense_to_void(matrix: torch.Tensor, tile_size: int = 32, threshold: float = 0.0) -> VOIDTensor:
+    """Dense -> VOID on the GPU (void/format.py:352-446): tiles whose L1 norm exceeds ``threshold`` are kept,
+    in ascending Morton order.  ``matrix`` is a CUDA tensor of float32, float16 or bfloat16."""
+    assert matrix.dim() == 2, "Input must be 2D tensor"
+    _lib.require_cuda(matrix)
+    if tile_size != 32:
+        raise NotImplementedError("void_b200 builds 32x32 tiles, got tile_size=%d" % tile_size)
+    if matrix.dtype not in _lib.ELEM_CODE:
+        raise _lib.VoidB200Error("dense_to_void takes float32, float16 or bfloat16, got %s" % matrix.dtype)
+    M, N = matrix.shape
+    dev = matrix.device
+    a = matrix if matrix.stride(1) == 1 and matrix.stride(0) >= max(N, 1) else matrix.contiguous()
+    elem, ld = _lib.ELEM_CODE[a.dtype], a.stride(0) if M > 1 else max(N, 1)
+
+    def mark(lib, ws, ws_bytes, counts):
+        _lib.check(lib.void_dense_mark(_lib.ptr(a), elem, ld, M, N, float(threshold), _lib.ptr(ws), ws_bytes,
+                                       _lib.ptr(counts), _lib.stream_ptr(dev)), "void_dense_mark")
+
+    def fill(lib, ws, n_blocks, block_rows, block_cols, values):
+        _lib.check(lib.void_dense_gather(_lib.ptr(a), elem, ld, M, N, _lib.ptr(block_rows), _lib.ptr(block_cols),
+                                         n_blocks, _lib.ptr(values), _lib.stream_ptr(dev)), "void_dense_gather")
+
+    values, block_rows, block_cols, codes, n_blocks, nnz, grid = _build_on_device(mark, fill, M, N, dev, a.dtype)
+    return VOIDTensor(values=values, block_rows=block_rows, block_cols=block_cols, morton_codes=codes, shape=(M, N),
+                      tile_size=(32, 32), nnz_original=nnz, n_blocks=n_blocks,
+                      density=(n_blocks / grid) if n_blocks else 0.0, dtype=a.dtype)
+
+
+def _csr_to_void_device(matrix, dtype: torch.dtype, device) -> VOIDTensor:
+    """csr_to_void with the CSR arrays uploaded and everything else done by the CUDA library."""
+    M, N = matrix.shape
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    crow = torch.from_numpy(matrix.indptr.astype(np.int32)).to(dev)
+    col = torch.from_numpy(matrix.indices.astype(np.int32)).to(dev)
+    data = torch.from_numpy(matrix.data.astype(np.float32)).to(dev)
+
+    def mark(lib, ws, ws_bytes, counts):
+        _lib.check(lib.void_csr_mark(_lib.ptr(crow), _lib.ptr(col), M, N, _lib.ptr(ws), ws_bytes, _lib.ptr(counts),
+                                     _lib.stream_ptr(dev)), "void_csr_mark")
+
+    def fill(lib, ws, n_blocks, block_rows, block_cols, values):
+        _lib.check(lib.void_csr_scatter(_lib.ptr(crow), _lib.ptr(col), _lib.ptr(data), M, N, _lib.ptr(ws), n_blocks,
+                                        _lib.ptr(values), _lib.stream_ptr(dev)), "void_csr_scatter")
+
+    values, block_rows, block_cols, codes, n_blocks, _, grid = _build_on_device(mark, fill, M, N, dev, torch.float32)
+    if dtype != torch.float32:
+        values = values.to(dtype)
+    return VOIDTensor(values=values, block_rows=block_rows, block_cols=block_cols, morton_codes=codes, shape=(M, N),
+                      tile_size=(32, 32), nnz_original=matrix.nnz, n_blocks=n_blocks, density=n_blocks / grid, dtype=dtype)
+
+
 def csr_to_void(matrix, tile_size: int = 32, dtype: torch.dtype = torch.float32, device: str = "cpu",
                 warn_small_tiles: bool = True) -> VOIDTensor:
     """CSR -> VOID (void/format.py:248-349): active blocks are those holding a stored entry,
-    sorted by Morton code; the per-nonzero Python loop of the reference (:321-327) is one
-    vectorised scatter here, with the same "last write wins" result."""
+    sorted by Morton code.  For a CUDA ``device`` and 32x32 tiles the CSR arrays are uploaded and the
+    format is built there (void_csr_mark / void_morton_emit / void_csr_scatter); otherwise the
+    per-nonzero Python loop of the reference (:321-327) is one vectorised numpy scatter, with the
+    same "last write wins" result."""
     if warn_small_tiles and tile_size < MIN_TENSOR_CORE_TILE:
         warnings.warn(f"tile_size={tile_size} < {MIN_TENSOR_CORE_TILE}, Tensor Cores require K >= 16", UserWarning)
     if not sparse.isspmatrix_csr(matrix):
         matrix = sparse.csr_matrix(matrix)
     M, N = matrix.shape
+    if tile_size == 32 and torch.device(device).type == "cuda" and M > 0 and N > 0 and matrix.has_canonical_format \
+            and matrix.nnz < 2 ** 31:
+        return _csr_to_void_device(matrix, dtype, device)
     nbr = (M + tile_size - 1) // tile_size
     nbc = (N + tile_size - 1) // tile_size
     coo = matrix.tocoo()
