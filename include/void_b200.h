@@ -293,6 +293,26 @@ VOID_API int void_spmm_f8(const void_spmm_args* args, void_stream_t stream);
 VOID_API int void_spmm_fp(const void_spmm_args* args, int32_t kind, void_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Gradient of the floating-point product with respect to the stored tiles of A.  Replaces
+ * void_spmm_backward_a_kernel and its launch in VOIDSpMMFunction.backward,
+ * void/autograd.py:14-96, :196-219:
+ *     grad_tiles[i] = grad_out[32*br_i : 32*br_i+32, :] . b[32*bc_i : 32*bc_i+32, :]^T
+ * for the stored tiles only, fp32 accumulation, result in out_dtype.  (The other gradient,
+ * dB = A^T . dC, is void_spmm_fp on the transposed tensor, void/autograd.py:178-191.)
+ * grad_out [M, N] and b [K, N] are row-major of the element type of kind (VOID_KIND_TF32: fp32
+ * multiplied as TF32; VOID_KIND_F16 / VOID_KIND_BF16), 16-byte aligned, ldg / ldb in BYTES and
+ * multiples of 16.  items [n_items][4] int32 = (tile row, first packed tile, tile count <= 4, 0):
+ * groups of consecutive packed tiles of one tile row; tile_cols / block_indices as produced by
+ * void_pack_tiles_fp / void_build_tile_index; grad_tiles [nnz][32][32] is written at
+ * block_indices[packed position], i.e. in the order of the caller's tile list.
+ * ------------------------------------------------------------------------------------- */
+VOID_API int void_spmm_tile_grad(const void* grad_out, int64_t ldg, const void* b, int64_t ldb,
+                                 int32_t M, int32_t K, int32_t N, int32_t kind,
+                                 const int32_t* items, int32_t n_items, const int32_t* tile_cols,
+                                 const int32_t* block_indices, void* grad_tiles,
+                                 int32_t out_dtype, int32_t* status, void_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * void_spmm_i8 for callers that have no way to hand over scratch memory.  (This entry point has
  * no counterpart in the reference; it exists for embedders of this library.)
  *

@@ -274,6 +274,22 @@ def gelu_tanh_sigmoid(x):
     return (x * np.float32(0.5) * (np.float32(1.0) + t)).astype(np.float32)
 
 
+def spmm_backward(values, block_rows, block_cols, shape, b, grad_c):
+    """VOIDSpMMFunction.backward, void/autograd.py:160-221, in fp32: dL/dB = A^T @ dL/dC as the SpMM of the
+    transposed tensor (tiles transposed, block rows and columns swapped, :178-191); dL/dA_values[i] =
+    dL/dC[32 br : 32 br + 32, :] @ B[32 bc : 32 bc + 32, :]^T for the stored tiles only (:14-96), rows of dL/dC
+    and of B beyond the matrix read as zero (boundary_check)."""
+    M, K = shape
+    a = np.asarray(values, dtype=np.float32)
+    g = np.asarray(grad_c, dtype=np.float32)
+    bf = np.asarray(b, dtype=np.float32)
+    grad_b = spmm_fp(np.ascontiguousarray(a.transpose(0, 2, 1)), block_cols, block_rows, (K, M), g)
+    grad_values = np.zeros_like(a)
+    for i in range(len(block_rows)):
+        grad_values[i] = np.matmul(_b_block(g, int(block_rows[i]), M), _b_block(bf, int(block_cols[i]), K).T)
+    return grad_values, grad_b
+
+
 def silu(x):
     """_silu of void/fusion.py:53-56: x * sigmoid(x) in fp32."""
     x = np.asarray(x, dtype=np.float32)

@@ -22,6 +22,8 @@ Fixtures (all .npz, inputs included so that the tests do not depend on RNG stabi
 
   dense_small.npz    dense_to_void with and without a norm threshold on a ragged matrix
 
+  backward_small.npz gradients of VOIDSpMMFunction (dL/dA_values per stored tile, dL/dB) for a given dL/dC
+
 A fixture whose arrays come out identical to the file already present is left untouched.
 """
 import os
@@ -335,6 +337,20 @@ def main():
     empty = void.dense_to_void(torch.zeros(40, 50), tile_size=32)
     out["empty_meta"] = np.asarray([empty.n_blocks, empty.nnz_original], dtype=np.int64)
     save("dense_small.npz", **out)
+
+    # ---------------------------------------------------------------- backward_small
+    from void.autograd import VOIDSpMMFunction
+    rng = np.random.default_rng(47)
+    m = block_sparse_csr(rng, 6, 5, 0.5, M=180, K=150, empty_rows=(2,))
+    vt = void.csr_to_void(m, tile_size=32)
+    b = torch.from_numpy(rng.standard_normal((150, 72)).astype(np.float32)).requires_grad_(True)
+    grad_c = torch.from_numpy(rng.standard_normal((180, 72)).astype(np.float32))
+    vals = vt.values.clone().requires_grad_(True)
+    c = VOIDSpMMFunction.apply(vals, vt.block_rows, vt.block_cols, vt.shape, vt.tile_size, vt.n_blocks, b)
+    c.backward(grad_c)
+    save("backward_small.npz", **coo_inputs(m), b=b.detach().numpy(), grad_c=grad_c.numpy(),
+         block_rows=vt.block_rows.numpy(), block_cols=vt.block_cols.numpy(), c=c.detach().numpy(),
+         grad_values=vals.grad.numpy(), grad_b=b.grad.numpy())
 
 
 if __name__ == "__main__":

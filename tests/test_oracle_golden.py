@@ -115,6 +115,22 @@ def test_fp_spmm_c1_and_small():
     assert rel_err(total, g["stream_k"]) < 1e-6 and rel_err(g["stream_k"], g["c_fp32"]) < 1e-6
 
 
+def test_backward_matches_reference_autograd():
+    g = load_golden("backward_small.npz")
+    f = vo.csr_to_void_fields(coo_to_csr(g))
+    assert rel_err(vo.spmm_fp(f["values"], f["block_rows"], f["block_cols"], f["shape"], g["b"]), g["c"]) < 1e-6
+    gv, gb = vo.spmm_backward(f["values"], f["block_rows"], f["block_cols"], f["shape"], g["b"], g["grad_c"])
+    assert gv.shape == g["grad_values"].shape and rel_err(gv, g["grad_values"]) < 1e-6
+    assert gb.shape == (150, 72) and rel_err(gb, g["grad_b"]) < 1e-6
+    # against dense calculus: dB = A^T dC, and dA restricted to the stored tiles
+    a = coo_to_csr(g).toarray()
+    assert rel_err(gb, a.T @ g["grad_c"]) < 1e-5
+    full = np.zeros((192, 160), np.float32)
+    full[:180, :150] = g["grad_c"] @ g["b"].T
+    for i, (r, c) in enumerate(zip(f["block_rows"], f["block_cols"])):
+        assert np.allclose(gv[i], full[r * 32:(r + 1) * 32, c * 32:(c + 1) * 32], rtol=1e-4, atol=1e-4)
+
+
 def test_int8_spmm_small_cases():
     g = load_golden("int8_small.npz")
     shape = tuple(int(x) for x in g["shape"])

@@ -18,6 +18,7 @@ from .ops import void_spmm, void_spmv
 from .fusion import (ActivationType, FusedOpType, get_activation_code, void_spmm_gelu, void_spmm_relu, void_spmm_silu,
                      fused_sparse_mlp, FusedSparseOp, create_fused_spmm_gelu, create_fused_spmm_relu, create_sparse_mlp,
                      FusedSparseLinear)
+from .autograd import VOIDSpMMFunction, VOIDSpMM, SparseLinear, spmm_tile_grad, void_spmm_autograd
 from .stream_k import (StreamKWorkload, compute_stream_k_workload, void_spmm_stream_k, analyze_workload_balance)
 from .scheduler import WorkloadProfile, analyze_workload
 from .distributed import (ShardingStrategy, DistributedVOIDTensor, shard_void_tensor, distributed_void_spmm,

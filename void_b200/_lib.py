@@ -74,6 +74,8 @@ _PROTOTYPES = {
     "void_spmm_i8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
     "void_spmm_f8": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_vp]),
     "void_spmm_fp": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_i32, c_vp]),
+    "void_spmm_tile_grad": (ctypes.c_int, [c_vp, c_i64, c_vp, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp, c_i32, c_vp, c_vp,
+                                           c_vp, c_i32, c_vp, c_vp]),
     "void_spmm_i8_static_scratch": (ctypes.c_int, [ctypes.POINTER(SpmmArgs), c_i32, c_vp]),
 }
 

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libvoid_b200.so")
-SOURCES = ["spmm.cu", "prep.cu", "plan.cu", "format.cu"]
+SOURCES = ["spmm.cu", "prep.cu", "plan.cu", "format.cu", "tile_grad.cu"]
 HEADERS = [os.path.join(CSRC, "ptx.cuh"), os.path.join(HERE, "..", "include", "void_b200.h")]
 
 NVCC_FLAGS = [
