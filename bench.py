@@ -258,6 +258,13 @@ def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
             per_copy = workloads.algorithmic_bytes(w.nnz, w.shape[0] // 32, w.shape[1], N, w.shape[0], out.element_size(),
                                                    bq.element_size())
             n_copies = copies_hint if copies_hint > 0 else max(2, -(-2 * L2_BYTES // per_copy))
+            if world > 1:
+                # every rank must hold the same number of copies (one broadcast of B per copy follows);
+                # the realised tile count, and with it the bytes per copy, differs a little from rank to rank
+                import torch.distributed as dist
+                agreed = torch.tensor([n_copies], dtype=torch.int64, device=dev)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+                n_copies = int(agreed.item())
         del w
         i += 1
     info = {"name": None, "N": N, "out": out_dtype, "kind": kind}
@@ -285,7 +292,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that falls out of step ends the run in minutes, not in ten
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     if args.gpus != world and rank == 0:
         print("bench.py: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (args.gpus, world), file=sys.stderr)
 
