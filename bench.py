@@ -39,7 +39,7 @@ sys.path.insert(0, ROOT)
 METRIC = "block_sparse_spmm_tops_nonzero_tiles"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (C stays in the write-back L2 during a launch, so less than the algorithmic bytes)
-MEASURED_TRAFFIC = {"headline": 3.87e6, "fp8": 3.88e6, "powerlaw": 13.6e6}
+MEASURED_TRAFFIC = {"headline": 3.87e6, "fp8": 3.88e6, "powerlaw": 13.6e6, "fp32": 15.1e6}
 L2_BYTES = 126 * 1024 * 1024
 
 

@@ -74,6 +74,42 @@ def test_backward_vs_torch_dense_autograd(dtype):
     assert got.dtype == np.float32 and layer.values.grad.dtype == dtype and rel_err(got, ref) < tol
 
 
+def test_gradients_at_benchmark_size(capsys):
+    # 4096 x 4096 at 90 % block sparsity, N = 512: a sample of tile gradients and dB against dense products,
+    # and the two kernels' device times (shown with pytest -s)
+    w = workloads.headline(0.9, seed=0)
+    gc = torch.randn(4096, 512, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    a_t = void.VOIDTensor(w.a.values.permute(0, 2, 1).contiguous(), w.a.block_cols, w.a.block_rows, w.a.morton_codes,
+                          (4096, 4096), (32, 32), 0, w.a.n_blocks, 0.0)
+    grad_tiles = void.spmm_tile_grad(w.a, gc, w.b)
+    grad_b = void.void_spmm(a_t, gc)
+    void.check_device_status()
+    br, bc = _np(w.a.block_rows).astype(int), _np(w.a.block_cols).astype(int)
+    for i in np.random.default_rng(0).choice(w.a.n_blocks, 24, replace=False):
+        ref = gc[br[i] * 32:(br[i] + 1) * 32].double() @ w.b[bc[i] * 32:(bc[i] + 1) * 32].double().T
+        assert rel_err(_np(grad_tiles[i]), _np(ref)) < 2e-3
+    ref_b = w.a.to_dense().double().T[:, :1024] @ gc[:1024].double()
+    full_b = w.a.to_dense().T @ gc
+    assert rel_err(_np(grad_b), _np(full_b)) < 2e-3 and ref_b.shape == (4096, 512)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for _ in range(3):
+        void.spmm_tile_grad(w.a, gc, w.b)
+        void.void_spmm(a_t, gc, grad_b)
+    ev[0].record()
+    for _ in range(20):
+        void.spmm_tile_grad(w.a, gc, w.b)
+    ev[1].record()
+    for _ in range(20):
+        void.void_spmm(a_t, gc, grad_b)
+    ev[2].record()
+    torch.cuda.synchronize()
+    flops = 2.0 * w.a.n_blocks * 1024 * 512
+    with capsys.disabled():
+        print("\n[backward, 4096^2 90%% N=512 fp32] dA tiles %.1f us (%.1f TFLOP/s)  dB %.1f us (%.1f TFLOP/s)  "
+              "(host-launched, L2-warm)" % (ev[0].elapsed_time(ev[1]) * 50, flops / (ev[0].elapsed_time(ev[1]) * 50e-6) / 1e12,
+                                            ev[1].elapsed_time(ev[2]) * 50, flops / (ev[1].elapsed_time(ev[2]) * 50e-6) / 1e12))
+
+
 def test_sparse_linear_trains():
     # a few SGD steps on a regression target reduce the loss: gradients flow to the tiles and the bias
     mask = workloads.uniform_mask(4, 6, 0.5, seed=9)
