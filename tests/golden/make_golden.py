@@ -31,7 +31,9 @@ import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
 sys.dont_write_bytecode = True
-REF = os.environ.get("REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("REFERENCE_DIR")
+if not REF or not os.path.isdir(os.path.join(REF, "void")):
+    raise SystemExit("set REFERENCE_DIR to a checkout of the reference (the folder that holds void/)")
 sys.path.insert(0, REF)
 
 import numpy as np  # noqa: E402

@@ -1,35 +1,36 @@
-// Quantized block-sparse SpMM for B200 (sm_100a):  C = act(dequant(A_q . B_q) + bias).
+// Block-sparse SpMM for B200 (sm_100a):  C = act(dequant(A . B) + bias), A quantized to 8 bits (INT8 or
+// FP8 E4M3 with per-block scales) or floating point (fp16 / bf16, or fp32 multiplied as TF32).
 //
-// A is the packed VOID tensor (tile-row-major 32x32 8-bit tiles, each stored as 8x16-byte
-// core matrices), B is a row-major [K, N] 8-bit matrix.  The product is computed transposed
-// on the tensor cores so that the 32-row tile sits in the N slot of the instruction:
+// A is the packed VOID tensor (tile-row-major 32x32 tiles, each stored as 8-row x 16-byte core
+// matrices), B is a row-major [K, N] matrix of the same element size.  The product is computed
+// transposed on the tensor cores so that the 32-row tile sits in the N slot of the instruction:
 //
 //     D[n, m] (+)= sum_k  B[kcol*32 + k, n0 + n] * A_tile[m, k]        n < 128, m < 32, k < 32
 //
-// i.e. one tcgen05.mma (M=128, N=32, K=32) per (tile, 128-column panel of B).  The "A"
-// operand of the instruction is the B panel exactly as it lies in memory (n contiguous:
-// MN-major, 128-byte swizzle, written by a tiled TMA load); the "B" operand is the packed tile
-// (K-major, no swizzle, written by a linear bulk copy).  Accumulators live in tensor memory:
-// lane = output column n, column = tile row m.
+// i.e. tcgen05.mma (M=128, N=32, 32 bytes of k) once per (tile, 128-column panel of B) for 8-bit
+// elements, twice for 16-bit, four times for 32-bit.  The "A" operand of the instruction is the B
+// panel exactly as it lies in memory (n contiguous: MN-major, 128-byte swizzle, written by a tiled
+// TMA load); the "B" operand is the packed tile (K-major, no swizzle, written by a linear bulk
+// copy).  Accumulators live in tensor memory: lane = output column n, column = tile row m.
 //
-// Warp roles: warps 0..3 stream tiles and panels into a shared-memory ring, warp 4 issues the
-// MMAs, warps 5..12 read accumulators back (two warps per 32-lane TMEM quadrant, each taking
-// half of the 32 accumulator columns), apply scales / bias / activation and store C.
+// Warp roles (struct Shape): producer warps stream tiles and panels into a shared-memory ring, one
+// warp issues the MMAs and owns the tensor-memory allocation, epilogue warps read accumulators back
+// (one or two warps per 32-lane TMEM quadrant), apply scales / bias / activation and store C.
 //
 // The ring moves GROUPS of up to `group` consecutive tiles of a tile row per stage.  Measured on
 // B200, one turn of a stage by one thread (wait for the slot, expect_tx, issue the copies) costs
 // about 300 ns whatever the bytes, so the stream is latency-bound on the issuing thread, not on
 // the copy engine: a group needs one wait + one expect_tx + one bulk copy (its tiles are
 // contiguous in the packed store) and one tiled TMA per tile, the TMAs issued by different lanes
-// in the same instruction, and the four producer warps take the groups round-robin so that four
-// stage turns are in flight at once.  When N is a multiple of 128 the TMA is 3-D (B viewed as
-// [panel][k][128 columns]) and fetches all panels of the work item at once.
+// in the same instruction, and the producer warps take the groups round-robin so that several
+// stage turns are in flight at once.  When N is a whole number of 128-byte column blocks the TMA
+// is 3-D (B viewed as [column block][k][128 bytes]) and fetches all panels of the work item at once.
 //
 // Two kernels share this pipeline:
 //   spmm_rowacc_kernel  one accumulator per (tile row, column chunk), scaled once by the
-//                       row's mean tile scale (the INT8 semantic of void/int_quant.py:479-526);
-//                       rows cut into several segments by a work plan are finished by the
-//                       CTA that arrives last.
+//                       row's mean tile scale (the INT8 semantic of void/int_quant.py:479-526) or
+//                       not at all (floating point, void/ops.py:93-146); rows cut into several
+//                       segments by a work plan are finished by the CTA that arrives last.
 //   spmm_drain_kernel   every tile's product lands in its own TMEM slot and is folded into
 //                       registers with that tile's scale (the FP8 semantic of
 //                       void/fp8.py:638-659; also exact per-block INT8 dequantisation).
