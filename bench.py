@@ -488,6 +488,13 @@ def main():
             print("bench.py: e2e graph capture failed (%r), using the stream pipeline" % (ex,), file=sys.stderr)
             slot_graphs = None
 
+    if world > 1:
+        # the timed loops below hold a barrier each: every rank must take the same ones
+        okf = torch.tensor([1 if slot_graphs is not None else 0], dtype=torch.int64, device=dev)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        if int(okf.item()) == 0:
+            slot_graphs = None
+
     def e2e_step_graph(i):
         sl = slots[i % DEPTH]
         gk, st_k = slot_graphs[i % DEPTH]
