@@ -49,6 +49,42 @@ def test_no_cpu_fallback():
         void.void_tensor_to_fp8(a)
 
 
+def test_floating_point_and_training_operators_refuse_cpu_tensors():
+    import scipy.sparse as sp
+    a = void.csr_to_void(sp.random(64, 96, density=0.2, format="csr", dtype=np.float32, random_state=2))
+    b = torch.randn(96, 8)
+    for call in (lambda: void.void_spmm(a, b), lambda: void.void_spmv(a, b[:, 0]), lambda: void.void_spmm_gelu(a, b),
+                 lambda: void.void_spmm_stream_k(a, b), lambda: void.dense_to_void(torch.randn(64, 64)),
+                 lambda: void.spmm_tile_grad(a, torch.randn(64, 8), b),
+                 lambda: void.fused_sparse_mlp(torch.randn(4, 96), a, a)):
+        with pytest.raises(_lib.VoidB200Error, match="no CPU path"):
+            call()
+
+
+def test_tile_grad_items_cover_every_tile_once():
+    # groups of at most four consecutive packed tiles, never across a tile row (host-side index arithmetic)
+    from void_b200.autograd import tile_grad_items
+    row_ptr = torch.tensor([0, 0, 5, 5, 6, 14, 14, 17], dtype=torch.int32)
+    items = tile_grad_items(row_ptr).numpy()
+    assert items.dtype == np.int32 and items.shape[1] == 4
+    assert items[:, :3].tolist() == [[1, 0, 4], [1, 4, 1], [3, 5, 1], [4, 6, 4], [4, 10, 4], [6, 14, 3]]
+    covered = np.concatenate([np.arange(t0, t0 + n) for _, t0, n, _ in items])
+    assert covered.tolist() == list(range(17))
+    assert tile_grad_items(torch.zeros(4, dtype=torch.int32)).shape == (0, 4)
+
+
+def test_product_kind_follows_the_operand_types():
+    from void_b200.ops import product_kind
+    import scipy.sparse as sp
+    a = void.csr_to_void(sp.random(64, 64, density=0.2, format="csr", dtype=np.float32, random_state=3))
+    assert product_kind(a, torch.zeros(64, 4)) == _lib.KIND_TF32
+    assert product_kind(a.half(), torch.zeros(64, 4, dtype=torch.float16)) == _lib.KIND_F16
+    assert product_kind(a.bfloat16(), torch.zeros(64, 4, dtype=torch.bfloat16)) == _lib.KIND_BF16
+    assert product_kind(a.half(), torch.zeros(64, 4)) == _lib.KIND_TF32          # mixed: through fp32, like the reference's casts
+    with pytest.raises(_lib.VoidB200Error):
+        product_kind(a, torch.zeros(64, 4, dtype=torch.int8))
+
+
 def test_package_never_imports_the_oracle():
     pkg = os.path.join(ROOT, "void_b200")
     for fn in os.listdir(pkg):
