@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define VOID_B200_ABI_VERSION 2
+#define VOID_B200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define VOID_API __attribute__((visibility("default")))
@@ -272,6 +272,15 @@ typedef struct void_spmm_args {
   /* [M] bias added per OUTPUT ROW before the activation, or NULL: the linear-layer form
    * act(W x + b[:, None]) of void_spmm_activation_row_bias_kernel, void/fusion.py:201-304 */
   const float* row_bias;
+  /* 1: B and C are stored TRANSPOSED - b is [N, K] row-major (k contiguous, ldb bytes between its
+   * rows n) and out is [N, M] row-major (ldc elements between its rows n).  This is the linear-layer
+   * form y = x W^T with activations x [batch, in] and results y [batch, out] used as they lie in
+   * memory, no transposed copies (the reference transposes both, void/fusion.py:586-598,
+   * void/autograd.py:336).  Index meanings are unchanged: col_scale / bias are per n, row_bias per m.
+   * Row-accumulate kernel only: not with VOID_SCALE_PER_TILE, FP8, a plan, acc_out or
+   * worker_partials; at most two panels per work item.  0: as described above.               */
+  int32_t transposed;
+  int32_t reserved;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

@@ -110,6 +110,32 @@ def test_gradients_at_benchmark_size(capsys):
                                             ev[1].elapsed_time(ev[2]) * 50, flops / (ev[1].elapsed_time(ev[2]) * 50e-6) / 1e12))
 
 
+def test_sparse_linear_gradients_vs_torch_linear():
+    mask = workloads.uniform_mask(5, 7, 0.5, seed=4)
+    w = workloads.block_sparse(mask, 8, seed=4)
+    lin = void.SparseLinear(224, 160, w.a, bias=True)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    with torch.no_grad():
+        lin.bias.copy_(torch.randn(160, device="cuda", generator=gen))
+    x = torch.randn(3, 50, 224, device="cuda", generator=gen, requires_grad=True)
+    gy = torch.randn(3, 50, 160, device="cuda", generator=gen)
+    y = lin(x)
+    y.backward(gy)
+    dense = w.a.to_dense().clone().requires_grad_(True)
+    x_ref = x.detach().clone().requires_grad_(True)
+    b_ref = lin.bias.detach().clone().requires_grad_(True)
+    torch.nn.functional.linear(x_ref, dense, b_ref).backward(gy)
+    assert y.shape == (3, 50, 160) and y.is_contiguous()
+    assert rel_err(_np(y), _np(torch.nn.functional.linear(x_ref, dense, b_ref))) < 2e-3
+    assert rel_err(_np(x.grad), _np(x_ref.grad)) < 2e-3
+    assert rel_err(_np(lin.bias.grad), _np(b_ref.grad)) < 1e-5
+    br, bc = _np(w.a.block_rows).astype(int), _np(w.a.block_cols).astype(int)
+    full = _np(dense.grad)
+    ref = np.stack([full[r * 32:(r + 1) * 32, c * 32:(c + 1) * 32] for r, c in zip(br, bc)])
+    assert rel_err(_np(lin.sparse_weight.values.grad), ref) < 2e-3
+    void.check_device_status()
+
+
 def test_sparse_linear_trains():
     # a few SGD steps on a regression target reduce the loss: gradients flow to the tiles and the bias
     mask = workloads.uniform_mask(4, 6, 0.5, seed=9)

@@ -94,7 +94,8 @@ def test_row_bias_mlp_and_linear_module_vs_reference_output():
     lin = void.FusedSparseLinear(270, 200, w1, activation="gelu", bias=True)
     with torch.no_grad():
         lin.bias.copy_(b1)
-    assert torch.equal(lin(x), h.T) and "in_features=270" in repr(lin)
+    assert torch.allclose(lin(x), h.T, rtol=1e-6, atol=1e-6) and "in_features=270" in repr(lin)
+    assert lin(x).is_contiguous()
     with pytest.raises(AssertionError):
         _void_spmm_activation_row_bias(w1, b, b2, None, "gelu")            # wrong bias length
     # the same epilogue on the quantized kernel (extension): bias per row after dequantisation
@@ -103,6 +104,36 @@ def test_row_bias_mlp_and_linear_module_vs_reference_output():
     pre = void.void_spmm_int8(q, bq, bs)
     got = _void_spmm_activation_row_bias(q, bq, b1, None, "relu", b_scale=bs)
     assert torch.allclose(got, torch.relu(pre + b1[:, None]), rtol=1e-6, atol=1e-6)
+    void.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int8])
+@pytest.mark.parametrize("batch", [1, 100, 128, 300])
+def test_linear_without_transposes_exact_on_small_integers(dtype, batch):
+    # y = x @ A^T with x [batch, in] and y [batch, out] as they lie in memory; small integers are exact in every
+    # kind, so any slip in the K-major operand layout (swizzle span of 32 / 64 / 128 bytes) shows as a wrong integer
+    mask = workloads.uniform_mask(7, 9, 0.5, seed=batch)
+    mask[2] = False
+    gen = torch.Generator().manual_seed(batch)
+    tiles = torch.randint(-3, 4, (int(mask.sum()), 32, 32), generator=gen).float()
+    a = void.void_from_block_mask(mask, tiles, shape=(200, 270), device="cuda")     # ragged out / in features
+    x = torch.randint(-3, 4, (batch, 270), generator=gen).float().cuda()
+    ref = x @ a.to_dense().T
+    bias = torch.randint(-5, 6, (200,), generator=gen).float().cuda()
+    if dtype == torch.int8:
+        q = void.quantize_void_tensor(a)
+        xs = torch.rand(batch, generator=gen).cuda() + 0.5
+        y = void.void_linear(q, x.to(torch.int8), bias, 1, x_scale=xs)
+        ref_q = void.void_spmm_int8(q, x.to(torch.int8).T.contiguous(), xs, bias=None, row_bias=bias, activation=1).T
+        assert y.shape == (batch, 200) and y.dtype == torch.float32 and torch.equal(y, ref_q)
+    else:
+        y = void.void_linear(a.to_dtype(dtype), x.to(dtype), out=torch.empty(batch, 200, device="cuda"))
+        assert torch.equal(y, ref)
+        yb = void.void_linear(a.to_dtype(dtype), x.to(dtype), bias, 1)
+        assert yb.dtype == dtype and torch.equal(yb.float(), torch.relu(ref + bias[None, :]).to(dtype).float())
+        wide = torch.full((batch, 264), 9.0, device="cuda")                         # output rows with a larger pitch
+        void.void_linear(a.to_dtype(dtype), x.to(dtype), out=wide[:, :200])
+        assert torch.equal(wide[:, :200], ref) and bool((wide[:, 200:] == 9.0).all())
     void.check_device_status()
 
 

@@ -14,11 +14,11 @@ from .int_quant import (IntFormat, ScaleMode, IntQuantConfig, QuantizationParams
                         get_quantization_error, quantize_cols_int8)
 from .fp8 import (FP8Format, FP8Config, FP8ScalingInfo, FP8VOIDTensor, create_scaling_info, compute_amax,
                   quantize_to_fp8, dequantize_from_fp8, void_spmm_fp8, void_tensor_to_fp8, quantize_cols_fp8)
-from .ops import void_spmm, void_spmv
+from .ops import void_spmm, void_spmv, void_linear
 from .fusion import (ActivationType, FusedOpType, get_activation_code, void_spmm_gelu, void_spmm_relu, void_spmm_silu,
                      fused_sparse_mlp, FusedSparseOp, create_fused_spmm_gelu, create_fused_spmm_relu, create_sparse_mlp,
                      FusedSparseLinear)
-from .autograd import VOIDSpMMFunction, VOIDSpMM, SparseLinear, spmm_tile_grad, void_spmm_autograd
+from .autograd import VOIDSpMMFunction, VOIDLinearFunction, VOIDSpMM, SparseLinear, spmm_tile_grad, void_spmm_autograd
 from .stream_k import (StreamKWorkload, compute_stream_k_workload, void_spmm_stream_k, analyze_workload_balance)
 from .scheduler import WorkloadProfile, analyze_workload
 from .distributed import (ShardingStrategy, DistributedVOIDTensor, shard_void_tensor, distributed_void_spmm,

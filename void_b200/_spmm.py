@@ -197,17 +197,19 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
          grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None, flags: int = 0,
-         row_bias=None) -> torch.Tensor:
-    """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device."""
+         row_bias=None, transposed: bool = False) -> torch.Tensor:
+    """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device.
+    With ``transposed`` b is [N, K] and out is [N, M]: the product is out = b @ A^T, both used as they lie."""
     lib = _lib.load()
     _lib.require_cuda(b, out, packed.tiles)
     dev = b.device
     M, K = packed.shape
-    N = b.shape[1]
-    if b.shape[0] != K:
+    N = b.shape[0] if transposed else b.shape[1]
+    if (b.shape[1] if transposed else b.shape[0]) != K:
         raise _lib.VoidB200Error("shape mismatch: A is %s, B is %s" % (packed.shape, tuple(b.shape)))
-    if tuple(out.shape) != (M, N) or out.stride(1) != 1:
-        raise _lib.VoidB200Error("out must be a row-major [%d, %d] tensor" % (M, N))
+    want = (N, M) if transposed else (M, N)
+    if tuple(out.shape) != want or out.stride(1) != 1:
+        raise _lib.VoidB200Error("out must be a row-major [%d, %d] tensor" % want)
     if out.dtype not in _lib.OUT_DTYPE_CODE:
         raise _lib.VoidB200Error("unsupported output dtype %s" % out.dtype)
     es = _lib.KIND_ELEM_BYTES[packed.kind]
@@ -252,6 +254,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     a.panels_per_item, a.stages, a.grid, a.tiles_per_stage = panels_per_item, stages, grid, tiles_per_stage
     a.trace = None if trace is None else trace.data_ptr()
     a.cta_shape = cta_shape
+    a.transposed = 1 if transposed else 0
     a.flags = flags
     with torch.cuda.device(dev):
         if es > 1:

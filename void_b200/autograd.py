@@ -125,6 +125,43 @@ class VOIDSpMMFunction(Function):
         return grad_a_values, None, None, None, None, None, grad_b
 
 
+class VOIDLinearFunction(Function):
+    """y = x @ A^T (+ bias) for x [batch, in]: the linear layer on activations as they lie in memory
+    (ops.void_linear), differentiable in A's stored tiles, x and the bias.
+        dL/dx        = dL/dy @ A          - void_linear with the transposed tensor
+        dL/dA_values = (dL/dy)^T @ x      - for the stored tiles only (void_spmm_tile_grad; its operands need
+                                            the batch index contiguous, so dL/dy and x are transposed here)
+        dL/dbias     = column sums of dL/dy
+    The reference's SparseLinear computes (A @ x^T)^T through VOIDSpMMFunction and adds the bias as a
+    separate op (void/autograd.py:320-344)."""
+
+    @staticmethod
+    def forward(ctx: Any, a_values, a_block_rows, a_block_cols, a_shape, a_tile_size, a_n_blocks: int, x, bias):
+        a = _bare_void(a_values.detach(), a_block_rows, a_block_cols, a_shape, a_tile_size, a_n_blocks)
+        y = ops.void_linear(a, x.detach(), None if bias is None else bias.detach())
+        ctx.save_for_backward(a_values, a_block_rows, a_block_cols, x)
+        ctx.a_shape, ctx.a_tile_size, ctx.a_n_blocks = tuple(a_shape), tuple(a_tile_size), a_n_blocks
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, grad_output: torch.Tensor):
+        a_values, a_block_rows, a_block_cols, x = ctx.saved_tensors
+        M, K = ctx.a_shape
+        grad_output = grad_output.contiguous()
+        grad_a_values = grad_x = grad_bias = None
+        if ctx.needs_input_grad[6]:
+            a_t = _bare_void(a_values.detach().permute(0, 2, 1).contiguous(), a_block_cols, a_block_rows, (K, M),
+                             ctx.a_tile_size[::-1], ctx.a_n_blocks)
+            grad_x = ops.void_linear(a_t, grad_output.to(x.dtype)) if ctx.a_n_blocks else torch.zeros_like(x)
+        if ctx.needs_input_grad[0]:
+            a = _bare_void(a_values.detach(), a_block_rows, a_block_cols, ctx.a_shape, ctx.a_tile_size, ctx.a_n_blocks)
+            grad_a_values = spmm_tile_grad(a, grad_output.T.contiguous(), x.detach().T.contiguous())
+        if ctx.has_bias and ctx.needs_input_grad[7]:
+            grad_bias = grad_output.sum(0)
+        return grad_a_values, None, None, None, None, None, grad_x, grad_bias
+
+
 class VOIDSpMM(torch.nn.Module):
     """A VOID matrix as a module with a differentiable y = A @ x (void/autograd.py:224-291)."""
 
@@ -168,9 +205,9 @@ class SparseLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         input_shape = x.shape
         x_flat = x.reshape(-1, self.in_features)
-        y = self.sparse_weight(x_flat.T).T
-        if self.bias is not None:
-            y = y + self.bias
+        w = self.sparse_weight
+        y = VOIDLinearFunction.apply(w.values, w.block_rows, w.block_cols, w.shape, w.tile_size, w.n_blocks, x_flat,
+                                     self.bias)
         return y.reshape(input_shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:
@@ -182,4 +219,4 @@ def void_spmm_autograd(a: VOIDTensor, b: torch.Tensor) -> torch.Tensor:
     return VOIDSpMMFunction.apply(a.values, a.block_rows, a.block_cols, a.shape, a.tile_size, a.n_blocks, b)
 
 
-__all__ = ["VOIDSpMMFunction", "VOIDSpMM", "SparseLinear", "spmm_tile_grad", "tile_grad_items", "void_spmm_autograd"]
+__all__ = ["VOIDSpMMFunction", "VOIDLinearFunction", "VOIDSpMM", "SparseLinear", "spmm_tile_grad", "tile_grad_items", "void_spmm_autograd"]

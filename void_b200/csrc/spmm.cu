@@ -290,6 +290,70 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
   }
 }
 
+// Transposed output (C stored as [N, M], m contiguous): the thread owns output row n and sixteen consecutive
+// columns m0 .. m0 + 15 of it, so the values leave in 16-byte stores.  bias_n is the bias of this n, the
+// per-m bias (o.row_bias) is the same for every thread of the warp.
+template <int KIND>
+__device__ __forceinline__ void finish16_tr(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+                                            float row_scale, float cs, float bias_n) {
+  if (n >= o.N) return;
+  const int c0 = row * kTile + m0;   // first output column (a row index of A)
+  const int cols = o.M - c0;         // columns left
+  if (cols <= 0) return;
+  float v[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
+    v[k] = (x * row_scale) * cs + bias_n;
+  }
+  if (o.row_bias != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+      if (k < cols) v[k] += __ldg(o.row_bias + c0 + k);
+  }
+  if (o.act != VOID_ACT_NONE) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (o.act == VOID_ACT_GELU) v[k] = gelu_tanh_sigmoid(v[k]);
+      else if (o.act == VOID_ACT_RELU) v[k] = fmaxf(v[k], 0.0f);
+      else v[k] = v[k] * fast_sigmoid(v[k]);
+    }
+  }
+  const size_t first = (size_t)n * o.ldc + c0;
+  if (o.dtype == VOID_OUT_F32) {
+    float* dst = reinterpret_cast<float*>(o.out) + first;
+    if (cols >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+      for (int k = 0; k < 16; k += 4) *reinterpret_cast<float4*>(dst + k) = make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        if (k < cols) dst[k] = v[k];
+    }
+  } else {
+    uint32_t h[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (o.dtype == VOID_OUT_F16) {
+        const __half2 t = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+        h[k] = *reinterpret_cast<const uint32_t*>(&t);
+      } else {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+        h[k] = *reinterpret_cast<const uint32_t*>(&t);
+      }
+    }
+    uint16_t* dst = reinterpret_cast<uint16_t*>(o.out) + first;
+    if (cols >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<uint4*>(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        if (k < cols) dst[k] = (uint16_t)(h[k >> 1] >> ((k & 1) * 16));
+    }
+  }
+}
+
 struct __align__(8) PipeBars {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -309,7 +373,7 @@ __device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
 
 // Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
 // consumes them; group g uses ring stage g % stages and belongs to warp g % C::PW.
-template <class C, int ES>
+template <class C, int ES, bool TR = false>
 __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtensorMap* tmap, PipeBars* bars,
                                               uint32_t ring_base, uint32_t stage_bytes, volatile int* abort_flag,
                                               int lane, int pw) {
@@ -324,7 +388,7 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     if (i + step < end) seg_next = load_seg(p, i + step);
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
-    const uint32_t unit_bytes = (uint32_t)((kTileBytes + (p.use3d ? p.np : npan) * kPanelBytes) * ES);
+    const uint32_t unit_bytes = (uint32_t)((kTileBytes + ((p.use3d && !TR) ? p.np : npan) * kPanelBytes) * ES);
     const int ngroups = (s.t1 - s.t0 + G - 1) / G;
     int k = pw - g % C::PW;
     if (k < 0) k += C::PW;
@@ -354,7 +418,11 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
       if (lane < gcnt) {
-        if (p.use3d) {
+        if (TR) {
+          // B stored transposed ([N, K], k contiguous): one box of 128 rows of n x 32 k per panel
+          for (int q = 0; q < npan; ++q)
+            tma_load_2d(sbase + panel_off<ES>(p, lane, q), tmap, col * kTile, n0 + q * kPanelN, full);
+        } else if (p.use3d) {
           tma_load_3d(sbase + panel_off<ES>(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np * ES, full);
         } else {
           // one copy per 128-byte-wide block of columns: ES blocks of 128 / ES columns per panel
@@ -475,7 +543,7 @@ __device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abor
 // ------------------------------------------------------------------------------------------
 // Row-accumulate kernel.
 // ------------------------------------------------------------------------------------------
-template <int KIND, class C>
+template <int KIND, class C, bool TR = false>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
                                                                const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -500,7 +568,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
-    producer_loop<C, ES>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
+    producer_loop<C, ES, TR>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
     if (warp == 0 && lane == 0) stamp(p, 2);
   } else if (warp == C::MMA) {
     if (lane == 0) {
@@ -514,7 +582,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       constexpr uint64_t kPanelStep = (kPanelBytes * ES) >> 4, kTileStep = (kTileBytes * ES) >> 4;
       // one MMA covers 32 bytes of k: 32 / ES k-rows of the panel (8-row groups 1024 bytes apart) and two
       // 16-byte k-chunks of the packed tile (128 bytes apart)
-      constexpr uint64_t kPanelKStep = (kPanelBytes / ES) >> 4, kTileKStep = 256 >> 4;
+      // (transposed B: the panel is K-major, 32 bytes of k lie inside one row of its swizzle atom)
+      constexpr uint64_t kPanelKStep = TR ? 2 : ((kPanelBytes / ES) >> 4), kTileKStep = 256 >> 4;
       int begin, end, step;
       seg_range(p, begin, end, step);
       int stage = 0;
@@ -611,6 +680,31 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll 1
       for (int q = 0; q < npan; ++q) {
         const int n = n_base + q * kPanelN;
+        if (TR) {  // transposed output: this thread's 32 values are contiguous in its output row n
+          float csq = p.b_scale, biasq = 0.0f;
+          if (n < p.N) {
+            if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+            if (p.bias != nullptr) biasq = __ldg(p.bias + n);
+          }
+#pragma unroll
+          for (int c = 0; c < C::COLS; c += 16) {
+            uint32_t r[16];
+            if (has) {
+              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) r[k] = 0u;
+            }
+            if (q == npan - 1 && c + 16 >= C::COLS) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+            }
+            finish16_tr<KIND>(od, s.row, n, m_first + c, r, rs, csq, biasq);
+          }
+          continue;
+        }
         float cs_next = p.b_scale, bias_next = 0.0f;
         if (q + 1 < npan && n + kPanelN < p.N) {
           if (p.col_scale != nullptr) cs_next = __ldg(p.col_scale + n + kPanelN) * p.b_scale;
@@ -994,13 +1088,20 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (a->scale_mode != VOID_SCALE_ROW_MEAN && a->scale_mode != VOID_SCALE_PER_TILE) return VOID_ERR_BAD_ARG;
   if (a->scale_mode == VOID_SCALE_PER_TILE && a->nnz > 0 && a->tile_scales == nullptr) return VOID_ERR_BAD_ARG;
   if ((long long)a->nbr * kTile < a->M) return VOID_ERR_SHAPE;
-  if (a->ldc < a->N) return VOID_ERR_SHAPE;
+  const bool tr = a->transposed != 0;
+  if (a->transposed != 0 && a->transposed != 1) return VOID_ERR_BAD_ARG;
+  if (a->ldc < (tr ? a->M : a->N)) return VOID_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(a->tiles) & 1023u) != 0) return VOID_ERR_ALIGN;
   if (kind < VOID_KIND_I8 || kind > VOID_KIND_TF32) return VOID_ERR_BAD_ARG;
   const int es = (kind == VOID_KIND_TF32) ? 4 : ((kind == VOID_KIND_F16 || kind == VOID_KIND_BF16) ? 2 : 1);
   const bool floating = es > 1;
-  if ((reinterpret_cast<uintptr_t>(a->b) & 15u) != 0 || (a->ldb & 15) != 0 || a->ldb < (long long)a->N * es)
+  if ((reinterpret_cast<uintptr_t>(a->b) & 15u) != 0 || (a->ldb & 15) != 0 ||
+      a->ldb < (long long)(tr ? a->K : a->N) * es)
     return VOID_ERR_ALIGN;
+  // transposed operands: row-accumulate kernel without a plan or raw-accumulator outputs
+  if (tr && (kind == VOID_KIND_F8E4M3 || a->scale_mode != VOID_SCALE_ROW_MEAN || a->segs != nullptr ||
+             a->acc_out != nullptr || a->worker_partials != nullptr))
+    return VOID_ERR_BAD_ARG;
   if (floating && (a->scale_mode != VOID_SCALE_ROW_MEAN || a->row_scale != nullptr)) return VOID_ERR_BAD_ARG;
 
   const DeviceInfo dev = device_info();
@@ -1026,6 +1127,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   // columns per row-accumulate CTA, 512 per SM)
   int shape = a->cta_shape;
   if (shape < 0 || shape > 2) return VOID_ERR_BAD_ARG;
+  if (tr && np > 2) return VOID_ERR_BAD_ARG;
+  if (tr && shape == 1) return VOID_ERR_BAD_ARG;  // built for the slim shape only
   if (shape == 0) shape = ((!drain && np <= 2) || (drain && np == 1)) ? 2 : 1;
   if (shape == 2 && (np > 2 || (drain && np > 1))) return VOID_ERR_BAD_ARG;
   const bool slim = (shape == 2);
@@ -1083,9 +1186,9 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.np = np;
   p.group = group;
   p.stages = stages;
-  p.use3d = (a->N % (kPanelN / es) == 0) ? 1 : 0;
+  p.use3d = (!tr && a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
-  p.prefetch = (a->flags & 1) ? 0 : 1;
+  p.prefetch = ((a->flags & 1) || tr) ? 0 : 1;
   p.n_items = a->nbr * n_chunks;
 
   // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
@@ -1104,11 +1207,15 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   } else {
     p.desc_hi_a = smem_desc_hi(1024, 1024, kLayoutSw128);
   }
-  if (kind == VOID_KIND_I8) p.idesc = instr_desc(/*c s32*/ 2, /*a s8*/ 1, /*b s8*/ 1, /*a MN*/ 1, /*b K*/ 0, 128, 32);
-  else if (kind == VOID_KIND_F8E4M3) p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, 1, 0, 128, 32);
-  else if (kind == VOID_KIND_F16) p.idesc = instr_desc(1, /*a f16*/ 0, /*b f16*/ 0, 1, 0, 128, 32);
-  else if (kind == VOID_KIND_BF16) p.idesc = instr_desc(1, /*a bf16*/ 1, /*b bf16*/ 1, 1, 0, 128, 32);
-  else p.idesc = instr_desc(1, /*a tf32*/ 2, /*b tf32*/ 2, 1, 0, 128, 32);
+  // Transposed B ([N, K], k contiguous) is a K-major operand: rows of 32 * es bytes (one swizzle span of 32,
+  // 64 or 128 bytes), groups of 8 rows 256 * es bytes apart.
+  const uint32_t a_mn = tr ? 0u : 1u;
+  if (tr) p.desc_hi_a = smem_desc_hi(16, 256 * es, es == 4 ? kLayoutSw128 : (es == 2 ? kLayoutSw64 : kLayoutSw32));
+  if (kind == VOID_KIND_I8) p.idesc = instr_desc(/*c s32*/ 2, /*a s8*/ 1, /*b s8*/ 1, a_mn, /*b K*/ 0, 128, 32);
+  else if (kind == VOID_KIND_F8E4M3) p.idesc = instr_desc(/*c f32*/ 1, /*a e4m3*/ 0, /*b e4m3*/ 0, a_mn, 0, 128, 32);
+  else if (kind == VOID_KIND_F16) p.idesc = instr_desc(1, /*a f16*/ 0, /*b f16*/ 0, a_mn, 0, 128, 32);
+  else if (kind == VOID_KIND_BF16) p.idesc = instr_desc(1, /*a bf16*/ 1, /*b bf16*/ 1, a_mn, 0, 128, 32);
+  else p.idesc = instr_desc(1, /*a tf32*/ 2, /*b tf32*/ 2, a_mn, 0, 128, 32);
 
   int grid;
   if (a->segs != nullptr) {
@@ -1135,7 +1242,17 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
                                    : (es == 2) ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     const int box_n = kPanelN / es;
     const CUtensorMapSwizzle swz = (es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
-    if (p.use3d) {
+    if (tr) {
+      //   transposed: dim0 = k, dim1 = n; box 32 k x 128 n, swizzle span = the 32 * es bytes of a row
+      const cuuint64_t gdim[2] = {(cuuint64_t)a->K, (cuuint64_t)a->N};
+      const cuuint64_t gstride[1] = {(cuuint64_t)a->ldb};
+      const cuuint32_t box[2] = {(cuuint32_t)kTile, (cuuint32_t)kPanelN};
+      const cuuint32_t estride[2] = {1, 1};
+      const CUtensorMapSwizzle sw = (es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B
+                                    : (es == 2) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+      r = enc(&tmap, dt, 2, const_cast<void*>(a->b), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (p.use3d) {
       const cuuint64_t gdim[3] = {(cuuint64_t)box_n, (cuuint64_t)a->K, (cuuint64_t)(a->N / box_n)};
       const cuuint64_t gstride[2] = {(cuuint64_t)a->ldb, (cuuint64_t)kPanelN};
       const cuuint32_t box[3] = {(cuuint32_t)box_n, (cuuint32_t)kTile, (cuuint32_t)(np * es)};
@@ -1145,7 +1262,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) p.use3d = 0;  // fall back to one 2-D copy per panel
     }
-    if (!p.use3d) {
+    if (!p.use3d && !tr) {
       const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->K};
       const cuuint64_t gstride[1] = {(cuuint64_t)a->ldb};
       const cuuint32_t box[2] = {(cuuint32_t)box_n, (cuuint32_t)kTile};
@@ -1162,7 +1279,11 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
     launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, p);                    \
   } while (0)
-  if (floating) {
+  if (tr) {
+    if (kind == VOID_KIND_TF32) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Slim, true>), Slim);
+    else if (kind == VOID_KIND_I8) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Slim, true>), Slim);
+    else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Slim, true>), Slim);
+  } else if (floating) {
     if (kind == VOID_KIND_TF32) {
       if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Slim>), Slim);
       else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Wide>), Wide);

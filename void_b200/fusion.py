@@ -20,7 +20,7 @@ from . import _lib
 from .format import VOIDTensor
 from .fp8 import FP8VOIDTensor, void_spmm_fp8
 from .int_quant import Int8VOIDTensor, void_spmm_int8
-from .ops import void_spmm
+from .ops import void_linear, void_spmm
 
 
 class FusedOpType(Enum):
@@ -108,12 +108,15 @@ def _void_spmm_activation_row_bias(a, b: torch.Tensor, bias: Optional[torch.Tens
 def fused_sparse_mlp(x: torch.Tensor, w1: VOIDTensor, w2: VOIDTensor, activation: str = "gelu",
                      bias1: Optional[torch.Tensor] = None, bias2: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = W2 @ activation(W1 @ x + b1) + b2 for x of shape [*, in_features] (void/fusion.py:557-602): two
-    launches, each with its bias and activation fused; the hidden activation stays [hidden, batch]
-    between them, so only the input and the result are transposed."""
+    launches, each with its bias and activation fused.  Activations stay [batch, features] throughout
+    (void_linear): none of the reference's three transposes is made."""
+    code = get_activation_code(activation)
+    if code > _lib.ACT_SILU:
+        raise NotImplementedError("activation %r is not fused on B200 (none, relu, gelu, silu are)" % activation)
     input_shape = x.shape
     x_2d = x.reshape(-1, x.shape[-1])
-    hidden = _void_spmm_activation_row_bias(w1, x_2d.T, bias1, None, activation)
-    out = _void_spmm_activation_row_bias(w2, hidden, bias2, None, "none").T
+    hidden = void_linear(w1, x_2d, bias1, code)
+    out = void_linear(w2, hidden, bias2, 0)
     return out.reshape(input_shape[:-1] + (out.shape[-1],))
 
 
@@ -189,7 +192,10 @@ class FusedSparseLinear(torch.nn.Module):
         input_shape = x.shape
         x_flat = x.reshape(-1, self.in_features)
         bias = None if self.bias is None else self.bias.detach()
-        y = _void_spmm_activation_row_bias(self.get_void_tensor(), x_flat.T, bias, None, self.activation).T
+        code = get_activation_code(self.activation)
+        if code > _lib.ACT_SILU:
+            raise NotImplementedError("activation %r is not fused on B200" % self.activation)
+        y = void_linear(self.get_void_tensor(), x_flat, bias, code)            # [batch, out], no transposes
         return y.reshape(input_shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:

@@ -74,6 +74,40 @@ def void_spmm(a: VOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
                       row_bias=row_bias, plan=plan, acc_out=acc_out, worker_partials=worker_partials)
 
 
+def void_linear(a, x: torch.Tensor, bias: Optional[torch.Tensor] = None, activation: int = 0,
+                out: Optional[torch.Tensor] = None, *, x_scale=None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = act(x @ A^T + bias) for activations x [batch, in] and a VOID weight A [out, in]: the linear layer
+    without transposed copies.  The reference computes (A @ x^T)^T and so copies x^T and returns a strided
+    view (void/fusion.py:586-598, :817-829; void/autograd.py:336); here the kernel reads x and writes y as
+    they lie in memory.  ``a`` is a floating VOIDTensor (y in x's dtype) or an Int8VOIDTensor (x int8 with
+    per-row scales ``x_scale`` [batch], or a float scalar; y fp32 unless ``out_dtype`` / ``out`` say otherwise).
+    ``bias`` has one value per output feature."""
+    from .int_quant import Int8VOIDTensor
+    assert x.dim() == 2 and x.shape[1] == a.shape[1], f"Dimension mismatch: A is {a.shape}, x is {tuple(x.shape)}"
+    _lib.require_cuda(a.values, x)
+    M = a.shape[0]
+    if bias is not None:
+        assert bias.shape == (M,), f"bias must have shape ({M},), got {tuple(bias.shape)}"
+    if isinstance(a, Int8VOIDTensor):
+        if x.dtype != torch.int8:
+            raise _lib.VoidB200Error("void_linear with an Int8VOIDTensor takes int8 activations, got %s" % x.dtype)
+        scalar, col_scale = (1.0, x_scale) if isinstance(x_scale, torch.Tensor) else (1.0 if x_scale is None else float(x_scale), None)
+        if out is None:
+            out = torch.empty(x.shape[0], M, dtype=out_dtype or torch.float32, device=x.device)
+        return _spmm.spmm(a.packed(), x, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=col_scale, b_scale=scalar,
+                          act=activation, row_bias=bias, transposed=True)
+    if x.dtype not in _lib.OUT_DTYPE_CODE:
+        raise _lib.VoidB200Error("void_linear: x must be float32, float16 or bfloat16, got %s" % x.dtype)
+    if out is None:
+        out = torch.empty(x.shape[0], M, dtype=x.dtype, device=x.device)
+    kind = product_kind(a, x)
+    packed = packed_fp(a, kind)
+    if x.dtype != _KIND_DTYPE[kind]:
+        x = x.to(_KIND_DTYPE[kind])
+    return _spmm.spmm(packed, x, out, scale_mode=_lib.SCALE_ROW_MEAN, use_row_scale=False, act=activation, row_bias=bias,
+                      transposed=True)
+
+
 def void_spmv(a: VOIDTensor, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = A @ x (void/ops.py:286-349): the one-column case of void_spmm."""
     squeeze_output = False
@@ -90,4 +124,4 @@ def void_spmv(a: VOIDTensor, x: torch.Tensor, out: Optional[torch.Tensor] = None
     return y.unsqueeze(1) if squeeze_output else y
 
 
-__all__ = ["void_spmm", "void_spmv"]
+__all__ = ["void_spmm", "void_spmv", "void_linear"]
