@@ -279,6 +279,8 @@ def main():
     if args.impl == "reference":
         cpu_reference_arm(args, rank, world)
         return
+    # stdout carries the one JSON line: NCCL writes its version banner and warnings to stdout unless told otherwise
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
     import numpy as np
     import torch
@@ -519,6 +521,39 @@ def main():
     sampler.stop_flag = True
     sampler.join(timeout=1.0)
 
+    # ---- first step after B appears on rank 0 (sharded workload, several ranks): broadcast of all of B and then
+    # the product, against B travelling in 256-column panels with every panel multiplied as it arrives
+    first_step = None
+    if world > 1 and args.workload == "sharded":
+        a_s, bq_s, bs_s, out_s = sets[0]
+        nbc = a_s.shape[1] // 32
+        dt_s = void.DistributedVOIDTensor(a_s, void.ShardingStrategy.ROW_WISE, world, rank, (info["M"], info["K"]),
+                                          (0, 0), (0, nbc))
+
+        def timed_once(fn):
+            torch.cuda.synchronize()
+            dist.barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            fn()
+            f1.record()
+            torch.cuda.synchronize()
+            return f0.elapsed_time(f1)
+
+        def serial():
+            void.broadcast_b(bq_s, src=0, scales=bs_s)
+            void.void_spmm_int8(a_s, bq_s, bs_s, out_s)
+
+        def overlapped():
+            void.broadcast_spmm_overlapped(dt_s, bq_s, bs_s, src=0, panel_cols=256, out=out_s)
+
+        for fn in (serial, overlapped):                 # warm both paths (allocations, NCCL channels)
+            timed_once(fn)
+        ts = torch.tensor([min(timed_once(serial) for _ in range(3)), min(timed_once(overlapped) for _ in range(3))],
+                          dtype=torch.float64, device=dev)
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        first_step = {"broadcast_then_spmm_ms": float(ts[0]), "overlapped_panels_ms": float(ts[1]), "panel_cols": 256}
+
     # ---- aggregate over ranks: max time, summed work
     t = torch.tensor([ms_total, e2e_ms, e2e_serial_ms], dtype=torch.float64, device=dev)
     work = torch.tensor([ops_per_step_local, float(np.mean(nnz_local))], dtype=torch.float64, device=dev)
@@ -564,7 +599,7 @@ def main():
             "config": {"workload": name, "M_per_gpu": M_local, "K": K, "N": N, "tile": 32,
                        "nnz_tiles": nnz_total, "out_dtype": str(sets[0][3].dtype).replace("torch.", ""),
                        "l2": "rotating_inputs", "input_copies": len(sets), "cuda_graph": not args.no_graph,
-                       "b_broadcast_ms": bcast_ms, "parallelism": "row_shards_x%d" % world},
+                       "b_broadcast_ms": bcast_ms, "first_step": first_step, "parallelism": "row_shards_x%d" % world},
             "roofline": roofline,
             "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h_b.numel() + h_s.numel() * 4),

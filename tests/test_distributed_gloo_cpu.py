@@ -60,7 +60,11 @@ def _worker(rank, world, port, ret):
         def oracle_local(local, b, b_scale, out_dtype, out=None):
             c = vo.spmm_int8(local.values.numpy(), local.scales.numpy(), local.block_rows.numpy(),
                              local.block_cols.numpy(), local.shape, b.numpy(), col_scale=b_scale.numpy())
-            return torch.from_numpy(c)
+            c = torch.from_numpy(c)
+            if out is not None:
+                out.copy_(c)
+                return out
+            return c
         vd._local_spmm = oracle_local
         shard = void.distributed_void_spmm(d, b_t, b_scale=s_t, gather_output=False)
         full = void.distributed_void_spmm(d, b_t, b_scale=s_t)            # all_gather, like the reference
@@ -68,6 +72,12 @@ def _worker(rank, world, port, ret):
         lo, hi = d.local_row_range
         assert np.array_equal(shard.numpy()[:min(hi * 32, shape[0]) - lo * 32], ref[lo * 32:hi * 32])
         assert full.shape == (shape[0], bq.shape[1]) and np.array_equal(full.numpy(), ref)
+        # first product with B arriving in column panels (ragged last panel): same shard, and B ends up everywhere
+        b2 = torch.from_numpy(bq).clone() if rank == 0 else torch.zeros_like(torch.from_numpy(bq))
+        s2 = torch.from_numpy(bs).clone() if rank == 0 else torch.zeros_like(torch.from_numpy(bs))
+        shard2, b2 = void.broadcast_spmm_overlapped(d, b2, s2, src=0, panel_cols=16)
+        assert np.array_equal(b2.numpy(), bq) and np.array_equal(s2.numpy(), bs)
+        assert shard2.shape == shard.shape and np.array_equal(shard2.numpy(), shard.numpy())
         ret[rank] = "ok"
     except Exception as e:  # pragma: no cover - surfaced through ret
         ret[rank] = repr(e)

@@ -33,6 +33,20 @@ def test_row_shards_concatenate_to_unsharded(world):
     void.check_device_status()
 
 
+def test_product_by_column_panels_equals_whole_product():
+    # the panel-wise first step (B arriving in column panels) on one rank: same bits as the one-launch product
+    mask = workloads.uniform_mask(40, 24, 0.7, seed=6)
+    w = workloads.block_sparse(mask, 416, seed=6)
+    q = void.quantize_void_tensor(w.a)
+    bq, bs = void.quantize_cols_int8(w.b)
+    full = void.void_spmm_int8(q, bq, bs, out_dtype=torch.float16)
+    d = void.shard_void_tensor(q, world_size=1, rank=0)
+    for cols in (128, 160, 416, 1000):
+        got, b_back = void.broadcast_spmm_overlapped(d, bq, bs, panel_cols=cols, out_dtype=torch.float16)
+        assert b_back is bq and torch.equal(got, full), cols
+    void.check_device_status()
+
+
 def test_fp8_and_float_tensors_shard_without_crashing():
     mask = workloads.uniform_mask(16, 16, 0.6, seed=9)
     w = workloads.block_sparse(mask, 64, seed=9)

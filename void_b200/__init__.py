@@ -22,7 +22,7 @@ from .autograd import VOIDSpMMFunction, VOIDLinearFunction, VOIDSpMM, SparseLine
 from .stream_k import (StreamKWorkload, compute_stream_k_workload, void_spmm_stream_k, analyze_workload_balance)
 from .scheduler import WorkloadProfile, analyze_workload
 from .distributed import (ShardingStrategy, DistributedVOIDTensor, shard_void_tensor, distributed_void_spmm,
-                          broadcast_b)
+                          broadcast_b, broadcast_spmm_overlapped)
 from ._lib import VoidB200Error, check_device_status
 
 __version__ = "0.1.0"

@@ -145,6 +145,84 @@ def _local_spmm(local, b, b_scale, out_dtype, out=None):
     raise NotImplementedError("distributed_void_spmm on B200 takes shards of Int8VOIDTensor or FP8VOIDTensor")
 
 
+def broadcast_spmm_overlapped(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, scales: Optional[torch.Tensor] = None,
+                              *, src: int = 0, panel_cols: int = 256, out: Optional[torch.Tensor] = None,
+                              out_dtype: Optional[torch.dtype] = None, group=None):
+    """The first product after B has been produced on rank ``src``: B travels in panels of ``panel_cols``
+    columns, and every rank multiplies a panel while the next one is still on the wire.
+
+    On entry ``b`` [K, N] (and ``scales`` [N]) hold data on rank ``src`` and are receive buffers of the same
+    shape elsewhere; on return every rank holds all of B, like after broadcast_b, and the local row shard of
+    C = A @ B is returned.  Panels are staged in contiguous [K, panel] buffers (a collective moves
+    contiguous bytes), broadcast on a side stream, multiplied on the current stream as they arrive
+    (the kernel takes the panel as its B and writes the matching columns of the row shard) and copied
+    into ``b``.  No kernel waits on another GPU: the order is kept by stream events on each rank.
+    """
+    local = dist_tensor.local_tensor
+    K, N = b.shape
+    rows = local.shape[0]
+    if out is None:
+        out = torch.empty(rows, N, dtype=out_dtype or torch.float32, device=b.device)
+    multi = is_distributed() and get_world_size() > 1
+    rank = get_rank() if multi else src
+    payload = b.view(torch.uint8) if b.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else b
+    if multi and scales is not None:
+        dist.broadcast(scales, src=src, group=group)
+    on_gpu = b.is_cuda
+    main = torch.cuda.current_stream(b.device) if on_gpu else None
+    side = _side_stream(b.device) if (on_gpu and multi) else None
+    if side is not None:
+        side.wait_stream(main)                         # B's producer ran on the current stream
+    staged = []
+    for c0 in range(0, N, panel_cols):
+        c1 = min(c0 + panel_cols, N)
+        ready = None
+        if multi:
+            ctx = torch.cuda.stream(side) if side is not None else _NullContext()
+            with ctx:
+                panel = torch.empty(K, c1 - c0, dtype=payload.dtype, device=b.device)
+                if rank == src:
+                    panel.copy_(payload[:, c0:c1])
+                dist.broadcast(panel, src=src, group=group)
+                if side is not None:
+                    ready = torch.cuda.Event()
+                    ready.record(side)
+            staged.append(panel)                       # stays alive until the streams are joined below
+            if ready is not None:
+                main.wait_event(ready)
+            if rank != src:
+                payload[:, c0:c1].copy_(panel)
+            panel_b = panel.view(b.dtype)
+        else:
+            panel_b = b[:, c0:c1]
+        sc = None if scales is None else scales[c0:c1]
+        _local_spmm(local, panel_b, sc, out.dtype, out[:, c0:c1])
+    if side is not None:
+        side.wait_stream(main)                         # the panels may be freed once the products have run
+    return out, b
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    """One communication stream per device, kept between calls: the caching allocator hands a freed staging
+    buffer back only to the stream it was allocated on, so a fresh stream per call would allocate anew each time."""
+    key = torch.device(device).index
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return st
+
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 def distributed_void_spmm(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                           async_op: bool = False, *, b_scale=None, out_dtype: Optional[torch.dtype] = None,
                           gather_output: bool = True) -> torch.Tensor:
@@ -180,4 +258,5 @@ def distributed_void_spmm(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, o
 
 
 __all__ = ["ShardingStrategy", "DistributedVOIDTensor", "shard_void_tensor", "distributed_void_spmm", "broadcast_b",
+           "broadcast_spmm_overlapped",
            "row_range", "is_distributed", "get_world_size", "get_rank"]
