@@ -37,6 +37,27 @@ def test_library_loads_and_reports_errors():
         _lib.check(-3, "x")
 
 
+def test_ctypes_mirror_matches_the_c_struct_layout(tmp_path):
+    # the header compiled as plain C: size and field offsets of void_spmm_args must be what the ctypes mirror assumes
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    fields = [name for name, _ in _lib.SpmmArgs._fields_]
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "void_b200.h"\nint main(void) {\n'
+                   '  printf("%zu\\n", sizeof(void_spmm_args));\n'
+                   + "".join('  printf("%%zu\\n", offsetof(void_spmm_args, %s));\n' % f for f in fields)
+                   + "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)],
+                   check=True)
+    out = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    assert out[0] == ctypes.sizeof(_lib.SpmmArgs)
+    assert out[1:] == [getattr(_lib.SpmmArgs, f).offset for f in fields]
+
+
 def test_no_cpu_fallback():
     import scipy.sparse as sp
     a = void.csr_to_void(sp.random(64, 64, density=0.2, format="csr", dtype=np.float32, random_state=1))
