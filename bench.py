@@ -623,6 +623,29 @@ def main():
             dt = (time.perf_counter() - t0) / n
             line["cpu_baseline"] = {"value": cfg["ops"] / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
                                     "sample": "whole workload x %d runs (%.1f s), float64-BLAS tile-row products" % (n, dt * n)}
+            if args.workload != "powerlaw":
+              try:
+                # the reference's only non-Triton compute path, its dispatch fallback torch.mm(a.to_dense(), B) in
+                # fp32 (void/dispatch.py:261-267), on the same host cores; to_dense is outside the timed region
+                dense = sets[0][0].to_dense().float().cpu() if hasattr(sets[0][0], "to_dense") else None
+                if dense is None:
+                    src = sets[0][0]
+                    vals = src.values.float() if hasattr(src, "values") else src.values_fp8.float()
+                    dense = void.VOIDTensor(vals, src.block_rows, src.block_cols, torch.zeros(0), src.shape, (32, 32),
+                                            0, src.n_blocks, 0.0).to_dense().cpu()
+                b_host = torch.randn(dense.shape[1], N)
+                torch.mm(dense, b_host)
+                t0 = time.perf_counter()
+                n = 0
+                while n < 50 and time.perf_counter() - t0 < 5.0:
+                    torch.mm(dense, b_host)
+                    n += 1
+                dtd = (time.perf_counter() - t0) / n
+                line["cpu_baseline"]["dense_fallback"] = {
+                    "ms": dtd * 1e3, "value": cfg["ops"] / dtd / 1e12, "unit": "TOPS over the nonzero tiles",
+                    "what": "torch.mm(a.to_dense(), B) fp32 on %d threads: the reference's dispatch fallback" % torch.get_num_threads()}
+              except Exception as ex:       # an extra datum: never let it take the bench line down
+                print("bench.py: dense fallback timing skipped (%r)" % (ex,), file=sys.stderr)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
