@@ -268,7 +268,8 @@ typedef struct void_spmm_args {
   /* debugging aid: when not NULL, 64 uint64 nanosecond timestamps per launched CTA      */
   void* trace;
   int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM) */
-  int32_t flags;           /* bit 0: do not prefetch the first work item into L2 (measurements)   */
+  int32_t flags;           /* measurement switches; bit 0: no L2 prefetch of the first work item;
+                              bit 1: no staged TMA store of 16-bit outputs (direct stores)          */
   /* [M] bias added per OUTPUT ROW before the activation, or NULL: the linear-layer form
    * act(W x + b[:, None]) of void_spmm_activation_row_bias_kernel, void/fusion.py:201-304 */
   const float* row_bias;

@@ -116,6 +116,33 @@ def test_int8_spmm_launch_shapes_agree():
     void.check_device_status()
 
 
+@pytest.mark.parametrize("case", [(16, 16, 256, 0, torch.float16, 0), (9, 7, 200, 5, torch.bfloat16, 2),
+                                  (5, 5, 128, 31, torch.float16, 1), (4, 4, 8, 0, torch.bfloat16, 3)])
+def test_staged_tma_store_equals_direct_stores(case):
+    """16-bit outputs through the shared-memory staging tile and a clipped TMA store: same bits as the direct stores,
+    at ragged M and N, with biases and every activation, one and several work items per CTA."""
+    from void_b200 import _lib, _spmm
+    nbr, nbc, n, m_cut, dt, act = case
+    mask = workloads.uniform_mask(nbr, nbc, 0.6, seed=n)
+    mask[1] = False
+    w = workloads.block_sparse(mask, n, seed=n)
+    M = nbr * 32 - m_cut
+    a = void.VOIDTensor(w.a.values, w.a.block_rows, w.a.block_cols, w.a.morton_codes, (M, nbc * 32), (32, 32), 0,
+                        w.a.n_blocks, 0.0)
+    q = void.quantize_void_tensor(a)
+    bq, bs = void.quantize_cols_int8(w.b)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    bias, rb = torch.randn(n, device="cuda", generator=gen), torch.randn(M, device="cuda", generator=gen)
+    outs = []
+    for flags, grid, np_ in ((2, 0, 0), (0, 0, 0), (0, 3, 1), (0, 3, 2)):      # flags bit 1 = direct stores
+        out = torch.full((M, n), 7.0, dtype=dt, device="cuda")
+        _spmm.spmm(q.packed(), bq, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=bs, bias=bias, row_bias=rb, act=act,
+                   flags=flags, grid=grid, panels_per_item=np_)
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    void.check_device_status()
+
+
 def test_linearity_and_row_permutation_properties():
     """Size-independent checks at the headline size: the int32 accumulators are linear in B, and a
     result row block depends only on its own tile row."""

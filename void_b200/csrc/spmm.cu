@@ -108,6 +108,7 @@ struct SpmmParams {
   int stages;   // ring depth
   int use3d;    // B panels of a tile fetched by one 3-D TMA
   int prefetch; // L2 prefetch of the CTA's first work item
+  int tma_store;  // 16-bit outputs leave through a staging tile in shared memory and a tiled TMA store
   int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
   int n_items;  // without a plan: nbr * n_chunks
   unsigned long long desc_hi_a;  // B panel  (instruction operand A: MN-major, 128B swizzle)
@@ -287,6 +288,41 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
 #pragma unroll
     for (int k = 0; k < 16; ++k, dst += o.ldc)
       if (k < rows) *dst = v[k];
+  }
+}
+
+// Sixteen finished 16-bit values of output column n into the staging tile [32 m][128 n] in shared memory
+// (stage_col points at element [0][n - n0]); same arithmetic as finish16.
+template <int KIND>
+__device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+                                               float row_scale, float cs, float bias, uint16_t* stage_col) {
+  float v[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[k]) : __uint_as_float(r[k]);
+    v[k] = (x * row_scale) * cs + bias;
+  }
+  const int r0 = row * kTile + m0;
+  const int rows = o.M - r0;
+  if (o.row_bias != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+      if (k < rows) v[k] += __ldg(o.row_bias + r0 + k);
+  }
+  if (o.act != VOID_ACT_NONE) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (o.act == VOID_ACT_GELU) v[k] = gelu_tanh_sigmoid(v[k]);
+      else if (o.act == VOID_ACT_RELU) v[k] = fmaxf(v[k], 0.0f);
+      else v[k] = v[k] * fast_sigmoid(v[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    uint16_t h;
+    if (o.dtype == VOID_OUT_F16) h = __half_as_ushort(__float2half_rn(v[k]));
+    else h = __bfloat16_as_ushort(__float2bfloat16_rn(v[k]));
+    stage_col[(m0 + k) * kPanelN] = h;
   }
 }
 
@@ -545,6 +581,7 @@ __device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abor
 // ------------------------------------------------------------------------------------------
 template <int KIND, class C, bool TR = false>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
+                                                               const __grid_constant__ CUtensorMap tmap_c,
                                                                const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
@@ -649,6 +686,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
     const int m_first = half * C::COLS;
     const OutDesc od = out_desc(p);
+    // staging tile of the TMA-store epilogue: behind the ring
+    const uint32_t stage_u32 = ring_base + (uint32_t)p.stages * stage_bytes;
+    uint16_t* stage_tile = reinterpret_cast<uint16_t*>(smem_raw + (stage_u32 - smem_u32(smem_raw)));
+    bool store_pending = false;
     int begin, end, step;
     seg_range(p, begin, end, step);
     uint32_t it = 0;
@@ -680,6 +721,45 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll 1
       for (int q = 0; q < npan; ++q) {
         const int n = n_base + q * kPanelN;
+        if (!TR && p.tma_store) {
+          // 16-bit outputs: the 32 x 128 result tile is put together in shared memory and leaves in one
+          // tiled store; the copy engine clips it at the edges of C.  The staging tile is free again once
+          // the previous store has read it.
+          if (store_pending) {
+            if (epi_tid == 0) bulk_wait_read();
+            asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
+          }
+          float csq = p.b_scale, biasq = 0.0f;
+          if (n < p.N) {
+            if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+            if (p.bias != nullptr) biasq = __ldg(p.bias + n);
+          }
+#pragma unroll
+          for (int c = 0; c < C::COLS; c += 16) {
+            uint32_t r[16];
+            if (has) {
+              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) r[k] = 0u;
+            }
+            if (q == npan - 1 && c + 16 >= C::COLS) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+            }
+            finish16_stage<KIND>(od, s.row, n, m_first + c, r, rs, csq, biasq, stage_tile + quad * 32 + lane);
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
+          if (epi_tid == 0) {
+            tma_store_2d(&tmap_c, stage_u32, (s.chunk * p.np + q) * kPanelN, s.row * kTile);
+            bulk_commit();
+          }
+          store_pending = true;
+          continue;
+        }
         if (TR) {  // transposed output: this thread's 32 values are contiguous in its output row n
           float csq = p.b_scale, biasq = 0.0f;
           if (n < p.N) {
@@ -825,6 +905,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         }
       }
     }
+    if (store_pending && epi_tid == 0) bulk_wait_all();  // the last tile has left shared memory and reached C
     if (epi_tid == 0) stamp(p, 6);
   }
   pipeline_teardown<C>(p, &abort_s, tmem_base, tmem_cols);
@@ -1061,9 +1142,8 @@ static int ensure_smem(const void* kernel, int bytes) {
   return 0;
 }
 
-template <typename Kernel>
-static void launch_pdl(Kernel kernel, int grid, int threads, int smem_bytes, cudaStream_t stream,
-                       const CUtensorMap& tmap, const SpmmParams& p) {
+template <typename Kernel, typename... Args>
+static void launch_pdl(Kernel kernel, int grid, int threads, int smem_bytes, cudaStream_t stream, const Args&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)threads);
@@ -1074,7 +1154,7 @@ static void launch_pdl(Kernel kernel, int grid, int threads, int smem_bytes, cud
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaLaunchKernelEx(&cfg, kernel, tmap, p);
+  cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
@@ -1152,7 +1232,13 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
   // hold at least one stage per producer warp.
   if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
-  const int smem_bytes = stages * stage_bytes + 1024;
+  // 16-bit outputs of the slim row-accumulate kernel leave through a staging tile (32 x 128 x 2 bytes behind the
+  // ring) and a tiled TMA store, when C qualifies as a tensor for the copy engine (16-byte aligned base and pitch)
+  const bool tma_store = !drain && !tr && slim && a->segs == nullptr && a->acc_out == nullptr &&
+                         a->worker_partials == nullptr && (a->flags & 2) == 0 &&
+                         (a->out_dtype == VOID_OUT_F16 || a->out_dtype == VOID_OUT_BF16) &&
+                         (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0 && ((a->ldc * 2) & 15) == 0;
+  const int smem_bytes = stages * stage_bytes + 1024 + (tma_store ? kTile * kPanelN * 2 : 0);
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
   SpmmParams p;
@@ -1189,6 +1275,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.use3d = (!tr && a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
   p.prefetch = ((a->flags & 1) || tr) ? 0 : 1;
+  p.tma_store = tma_store ? 1 : 0;
   p.n_items = a->nbr * n_chunks;
 
   // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
@@ -1274,30 +1361,49 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (r != CUDA_SUCCESS) return VOID_ERR_TENSOR_MAP;
   }
 
+  CUtensorMap tmap_c;
+  memset(&tmap_c, 0, sizeof(tmap_c));
+  if (tma_store) {
+    PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode();
+    if (enc == nullptr) return VOID_ERR_CUDA;
+    const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)a->ldc * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile};
+    const cuuint32_t estride[2] = {1, 1};
+    if (enc(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a->out, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return VOID_ERR_TENSOR_MAP;
+  }
+
 #define VB_LAUNCH(KERNEL, SHAPE)                                                               \
   do {                                                                                        \
     if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
     launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, p);                    \
   } while (0)
+#define VB_LAUNCH_ROWACC(KERNEL, SHAPE)                                                        \
+  do {                                                                                        \
+    if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
+    launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, tmap_c, p);            \
+  } while (0)
   if (tr) {
-    if (kind == VOID_KIND_TF32) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Slim, true>), Slim);
-    else if (kind == VOID_KIND_I8) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Slim, true>), Slim);
-    else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Slim, true>), Slim);
+    if (kind == VOID_KIND_TF32) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_TF32, Slim, true>), Slim);
+    else if (kind == VOID_KIND_I8) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim, true>), Slim);
+    else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F16, Slim, true>), Slim);
   } else if (floating) {
     if (kind == VOID_KIND_TF32) {
-      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Slim>), Slim);
-      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_TF32, Wide>), Wide);
+      if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_TF32, Slim>), Slim);
+      else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_TF32, Wide>), Wide);
     } else {  // fp16 and bf16 differ in the instruction descriptor only
-      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Slim>), Slim);
-      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F16, Wide>), Wide);
+      if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F16, Slim>), Slim);
+      else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F16, Wide>), Wide);
     }
   } else if (!drain) {
     if (kind == VOID_KIND_I8) {
-      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
-      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_I8, Wide>), Wide);
+      if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
+      else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Wide>), Wide);
     } else {
-      if (slim) VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Slim>), Slim);
-      else VB_LAUNCH((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Wide>), Wide);
+      if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Slim>), Slim);
+      else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Wide>), Wide);
     }
   } else if (kind == VOID_KIND_I8) {
     if (np == 1 && slim) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim>), Slim);
@@ -1311,6 +1417,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     else VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 4, Wide>), Wide);
   }
 #undef VB_LAUNCH
+#undef VB_LAUNCH_ROWACC
   return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
 }
 
