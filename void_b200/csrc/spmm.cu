@@ -721,7 +721,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll 1
       for (int q = 0; q < npan; ++q) {
         const int n = n_base + q * kPanelN;
-        if (!TR && p.tma_store) {
+        if (!TR && p.tma_store && fast) {
           // 16-bit outputs: the 32 x 128 result tile is put together in shared memory and leaves in one
           // tiled store; the copy engine clips it at the edges of C.  The staging tile is free again once
           // the previous store has read it.
@@ -1234,7 +1234,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
   // 16-bit outputs of the slim row-accumulate kernel leave through a staging tile (32 x 128 x 2 bytes behind the
   // ring) and a tiled TMA store, when C qualifies as a tensor for the copy engine (16-byte aligned base and pitch)
-  const bool tma_store = !drain && !tr && slim && a->segs == nullptr && a->acc_out == nullptr &&
+  // (with a plan, whole-row segments take this route and the pieces of split rows the ordinary one)
+  const bool tma_store = !drain && !tr && slim && a->acc_out == nullptr &&
                          a->worker_partials == nullptr && (a->flags & 2) == 0 &&
                          (a->out_dtype == VOID_OUT_F16 || a->out_dtype == VOID_OUT_BF16) &&
                          (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0 && ((a->ldc * 2) & 15) == 0;
