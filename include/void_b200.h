@@ -1,5 +1,6 @@
 /*
- * void_b200 — C ABI of the B200 (sm_100a) quantized block-sparse SpMM path.
+ * void_b200 — C ABI of the B200 (sm_100a) block-sparse SpMM path: the quantized (INT8 / FP8) product and, on
+ * the same kernels, the floating-point product, its gradients and the on-device format build.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream, returns 0
  * (VOID_OK) or a negative status, never throws, never synchronises the stream and never
@@ -11,7 +12,7 @@
  * Vocabulary: a *tile* is one stored 32x32 block of A; a *tile row* is one row of the
  * block grid (32 matrix rows); a *panel* is a 32(k) x 128(n) slab of B; the *packed* form
  * of A is its tiles in tile-row-major order, 1024 bytes each, in the core-matrix order the
- * tensor cores read from shared memory.
+ * tensor cores read from shared memory (1024 * element bytes for the floating-point kinds).
  */
 #ifndef VOID_B200_H_
 #define VOID_B200_H_
