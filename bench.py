@@ -157,7 +157,7 @@ def cpu_reference_arm(args, rank, world):
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": cfg["dtype"], "data": "synthetic", "impl": "reference", "config": cfg["config"],
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
-                         "sample": "whole %s workload per step, %d steps" % (cfg["config"]["workload"], n)},
+                         "sample": "whole %s workload per step, %d steps, %s" % (cfg["config"]["workload"], n, cfg["how"])},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -180,6 +180,7 @@ def cpu_workload(args, np, torch, vo):
     vals = torch.randn(len(rows), 32, 32, generator=g).numpy()
     b = torch.randn(mask.shape[1] * 32, N, generator=g).numpy()
     shape = (mask.shape[0] * 32, mask.shape[1] * 32)
+    how = "numpy tile-row products (float64 BLAS for the integer sums)"
     if args.workload in ("fp32", "fp16"):
         np_dt = np.float32 if args.workload == "fp32" else np.float16
         vals_t, b_t = vals.astype(np_dt), b.astype(np_dt)
@@ -194,12 +195,15 @@ def cpu_workload(args, np, torch, vo):
     else:
         q, s = vo.quantize_int8_tiles(vals)
         bq, bs = vo.quantize_int8_cols(b)
+        # the C restatement (int8 x int8 -> int32, OpenMP over tile rows) when it could be built, else the numpy one
+        spmm = vo.spmm_int8_c if vo.c_library() is not None else vo.spmm_int8
+        how = "C / OpenMP int8 tile-row products" if vo.c_library() is not None else how
         if args.workload == "powerlaw":
-            run = lambda: vo.gelu_tanh_sigmoid(vo.spmm_int8(q, s, rows, cols, shape, bq, col_scale=bs))
+            run = lambda: vo.gelu_tanh_sigmoid(spmm(q, s, rows, cols, shape, bq, col_scale=bs))
         else:
-            run = lambda: vo.spmm_int8(q, s, rows, cols, shape, bq, col_scale=bs).astype(np.float16)
+            run = lambda: spmm(q, s, rows, cols, shape, bq, col_scale=bs).astype(np.float16)
         dtype = "i8"
-    cfg = {"ops": workloads.spmm_ops(len(rows), N), "dtype": dtype,
+    cfg = {"ops": workloads.spmm_ops(len(rows), N), "dtype": dtype, "how": how,
            "config": {"workload": name, "M": shape[0], "K": shape[1], "N": N, "tile": 32, "nnz_tiles": int(len(rows)),
                       "block_sparsity": 1.0 - len(rows) / mask.size}}
     return cfg, run, cores
@@ -622,7 +626,7 @@ def main():
                 n += 1
             dt = (time.perf_counter() - t0) / n
             line["cpu_baseline"] = {"value": cfg["ops"] / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
-                                    "sample": "whole workload x %d runs (%.1f s), float64-BLAS tile-row products" % (n, dt * n)}
+                                    "sample": "whole workload x %d runs (%.1f s), %s" % (n, dt * n, cfg["how"])}
             if args.workload != "powerlaw":
               try:
                 # the reference's only non-Triton compute path, its dispatch fallback torch.mm(a.to_dense(), B) in

@@ -246,6 +246,49 @@ def spmm_int8(values_q, scales, block_rows, block_cols, shape, b_q, b_scale=1.0,
     return out[:M].astype(np.float32)
 
 
+_C_LIB = None
+
+
+def c_library():
+    """The compiled C restatement (oracle/void_oracle_c.c), built on first use; None without a C compiler."""
+    global _C_LIB
+    if _C_LIB is None:
+        import ctypes
+        from . import build_c
+        try:
+            path = build_c.build()
+            _C_LIB = ctypes.CDLL(path) if path else False
+        except (OSError, RuntimeError):
+            _C_LIB = False
+        if _C_LIB:
+            vp, i32, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_float
+            _C_LIB.void_oracle_spmm_int8.restype = ctypes.c_int
+            _C_LIB.void_oracle_spmm_int8.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, f32, vp, vp, vp]
+    return _C_LIB or None
+
+
+def spmm_int8_c(values_q, scales, block_rows, block_cols, shape, b_q, b_scale=1.0, col_scale=None, want_acc=False):
+    """spmm_int8 (and, with want_acc, spmm_int8_acc) through the C restatement: int8 x int8 -> int32 arithmetic,
+    OpenMP over tile rows.  Same results as the numpy functions above; raises RuntimeError without the library."""
+    lib = c_library()
+    if lib is None:
+        raise RuntimeError("the C oracle is not available (no C compiler and no prebuilt library)")
+    nbr, nbc, row_ptr, bidx = _row_order(block_rows, block_cols, shape)
+    M, K = shape
+    N = b_q.shape[1]
+    vals = np.ascontiguousarray(values_q, dtype=np.int8)
+    sc = np.ascontiguousarray(scales, dtype=np.float32)
+    bc = np.ascontiguousarray(block_cols, dtype=np.int32)
+    b = np.ascontiguousarray(b_q, dtype=np.int8)
+    cs = None if col_scale is None else np.ascontiguousarray(col_scale, dtype=np.float32)
+    out = np.empty((M, N), dtype=np.float32)
+    acc = np.empty((nbr * TILE, N), dtype=np.int32) if want_acc else None
+    ptr = lambda a: None if a is None else a.ctypes.data
+    lib.void_oracle_spmm_int8(ptr(vals), ptr(sc), ptr(bc), ptr(row_ptr), ptr(bidx), nbr, M, K, N, ptr(b),
+                              float(b_scale), ptr(cs), ptr(acc), ptr(out))
+    return (out, acc) if want_acc else out
+
+
 def spmm_fp8(values_fp8, scales, block_rows, block_cols, shape, b, per_tensor=False):
     """fp32 result of void_spmm_fp8_kernel, void/fp8.py:624-659: for every tile of the row, in row
     order, acc += (float(A8) * scale) @ float(B block), all in fp32.  ``b`` is fp32 [K, N]."""

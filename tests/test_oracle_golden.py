@@ -148,6 +148,23 @@ def test_int8_spmm_small_cases():
     assert np.array_equal((acc.astype(np.float32) * np.repeat(rs, 32)[:, None])[:shape[0]], g["c_unit"])
 
 
+def test_c_restatement_equals_numpy_oracle_and_reference():
+    if vo.c_library() is None:
+        pytest.skip("no C compiler")
+    g = load_golden("int8_small.npz")                                   # ragged M / K / N, empty tile rows
+    shape = tuple(int(x) for x in g["shape"])
+    args = (g["a_q"], g["a_scales"], g["block_rows"], g["block_cols"], shape, g["b_q"])
+    out, acc = vo.spmm_int8_c(*args, want_acc=True)
+    assert np.array_equal(acc, vo.spmm_int8_acc(g["a_q"], g["block_rows"], g["block_cols"], shape, g["b_q"]))
+    assert np.array_equal(out, vo.spmm_int8(*args)) and rel_err(out, g["c_unit"]) < 1e-6
+    assert rel_err(vo.spmm_int8_c(*args, b_scale=float(g["b_scalar"][0])), g["c_scalar"]) < 1e-6
+    g = load_golden("c1_plumbing.npz")
+    f = vo.csr_to_void_fields(coo_to_csr(g))
+    c = vo.spmm_int8_c(g["a_q"], g["a_scales"], f["block_rows"], f["block_cols"], f["shape"], g["b_q"],
+                       col_scale=g["b_scales"])
+    assert rel_err(c, g["c_int8"]) < 1e-6
+
+
 def test_fp8_amax_known_answers():
     # the literal known-answer test of the reference, tests/test_fp8.py:133-150
     g = load_golden("fp8_small.npz")
