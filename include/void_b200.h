@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define VOID_B200_ABI_VERSION 3
+#define VOID_B200_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define VOID_API __attribute__((visibility("default")))
@@ -256,21 +256,35 @@ typedef struct void_spmm_args {
   int32_t n_cta;             /* CTAs the plan was made for; 0 without a plan             */
   void* partials;            /* n_counters * panels_per_item * 16 KiB of int32 row
                                 accumulators, ZERO before the first use; left zero again */
-  int64_t partials_bytes;
-  int32_t* counters;         /* [n_counters] zero before the first use; left zero again  */
+  int64_t partials_bytes;    /* size of partials; a segment whose counter index does not fit
+                                (index >= partials_bytes / (panels_per_item * 16 KiB)) is
+                                skipped and the status word reads 2                       */
+  int32_t* counters;         /* one per accumulator row of partials, zero before the first
+                                use; left zero again                                      */
   void* worker_partials;     /* optional [n_segs, 32, N] int32: every segment's own sum  */
-  /* device status word: 0, or a code written by a bounded wait that gave up             */
+  /* device status word: 0; 1 = a bounded wait gave up; 2 = a split row of the plan does not fit
+   * the scratch the caller provided                                                      */
   int32_t* status;
   /* launch shape; 0 = library default                                                   */
   int32_t panels_per_item; /* 128-column panels of B per work item: 1, 2 or 4            */
   int32_t stages;          /* shared-memory ring depth                                   */
   int32_t grid;            /* CTAs to launch without a plan                              */
   int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1, 2, 4 or 8      */
-  /* debugging aid: when not NULL, 64 uint64 nanosecond timestamps per launched CTA      */
+  /* diagnostics: NULL for every ordinary launch.  Not NULL selects a separately compiled diagnostic kernel
+   * (slim INT8 row-accumulate or one-panel FP8 per-tile only, else VOID_ERR_BAD_ARG) that writes 64
+   * uint64 nanosecond timestamps per launched CTA; the ordinary kernels contain none of that code.   */
   void* trace;
-  int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM) */
-  int32_t flags;           /* measurement switches; bit 0: no L2 prefetch of the first work item;
-                              bit 1: no staged TMA store of 16-bit outputs (direct stores)          */
+  int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM);
+                              per-tile kernel with one panel only: 3 = 7 warps, 3 per SM; 4 = 10 warps, 3 per SM;
+                              5 = 6 warps, 4 per SM */
+  int32_t flags;           /* bit 0: no L2 prefetch of the first work item; bit 1: no staged TMA store of
+                              16-bit outputs (direct stores);
+                              bit 2: the caller vouches that the packed A (tiles, tile_cols, tile_scales,
+                              row_ptr, row_scale) and the plan were completely written before any kernel
+                              still in flight on the stream started - they are then read BEFORE the wait on
+                              the previous kernel (programmatic dependent launch), which takes their
+                              latency off the launch.  B, the scales of B, the biases and C are never
+                              touched before that wait.                                               */
   /* [M] bias added per OUTPUT ROW before the activation, or NULL: the linear-layer form
    * act(W x + b[:, None]) of void_spmm_activation_row_bias_kernel, void/fusion.py:201-304 */
   const float* row_bias;
@@ -282,7 +296,11 @@ typedef struct void_spmm_args {
    * Row-accumulate kernel only: not with VOID_SCALE_PER_TILE, FP8, a plan, acc_out or
    * worker_partials; at most two panels per work item.  0: as described above.               */
   int32_t transposed;
-  int32_t reserved;
+  /* 0 for every ordinary launch.  Test hooks: bits 0..15 = limit of every device-side wait in
+   * milliseconds (0: the default of 2000); bit 16 = the first group of tiles of each CTA is never
+   * delivered to the consumer, so that its wait runs out, the launch gives up in an orderly way and the
+   * status word reads 1 - used to test that path without any faulting or unbounded wait.            */
+  int32_t test_hooks;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);
@@ -352,6 +370,12 @@ VOID_API int void_spmm_tile_grad(const void* grad_out, int64_t ldg, const void* 
  * ------------------------------------------------------------------------------------- */
 VOID_API int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_split_rows,
                                          void_stream_t stream);
+
+/* Measurement aid (no counterpart in the reference): launches an empty kernel with the grid, block size,
+ * dynamic shared memory and launch attribute (programmatic stream serialisation) of an SpMM launch.  What
+ * a stream of such launches costs per launch is the part of an SpMM launch's time that no kernel code can
+ * remove; bench.py --workload floor reports it next to an SpMM over an empty A. */
+VOID_API int void_launch_floor(int32_t grid, int32_t threads, int32_t smem_bytes, void_stream_t stream);
 
 /* number of SMs of the current device (grid sizing on the host side) */
 VOID_API int void_device_sm_count(void);

@@ -400,8 +400,8 @@ def workload_balance(row_ptr):
 def shard_rows(block_rows, nbr, world_size, rank):
     """ROW_WISE shard of shard_void_tensor, void/distributed.py:115-125, :150-161, :170-172:
     rows_per_rank = ceil(nbr / world); rank owns block rows [start, end); kept tiles stay in their
-    original (Morton) order and get block_rows - start.  PARITY UNPINNED: the reference function
-    raises TypeError before returning, so this restatement has no reference output to compare."""
+    original (Morton) order and get block_rows - start.  A rank past the end gets start > end and no
+    tiles, as in the reference.  Pinned by shard_small.npz (reference output)."""
     rpr = (nbr + world_size - 1) // world_size
     start = rank * rpr
     end = min(start + rpr, nbr)
@@ -409,3 +409,31 @@ def shard_rows(block_rows, nbr, world_size, rank):
     mask = (block_rows >= start) & (block_rows < end)
     idx = np.nonzero(mask)[0]
     return start, end, idx, (block_rows[idx] - start).astype(np.int32)
+
+
+def shard(block_rows, block_cols, shape, world_size, rank, strategy, tile=32):
+    """shard_void_tensor for the three strategies, void/distributed.py:112-172.
+    ROW_WISE (:115-125): block rows [rank * ceil(nbr / world), ...), rows rebased (:160-161).
+    COLUMN_WISE (:127-137): block columns [rank * ceil(nbc / world), ...); block_cols are NOT rebased
+    (only rows are, :159-161) although the local shape shrinks to the range (:174-176).
+    BLOCK_WISE (:139-145): tile i of the stored order goes to rank i % world; ranges span the grid.
+    Returns a dict: ids (kept positions, stored order), rows, cols, row_range, col_range, shape."""
+    block_rows, block_cols = np.asarray(block_rows), np.asarray(block_cols)
+    M, K = int(shape[0]), int(shape[1])
+    nbr, nbc = (M + tile - 1) // tile, (K + tile - 1) // tile
+    if strategy == "row_wise":
+        start, end, idx, rows = shard_rows(block_rows, nbr, world_size, rank)
+        return {"ids": idx, "rows": rows, "cols": block_cols[idx].astype(np.int32), "row_range": (start, end),
+                "col_range": (0, nbc), "shape": ((end - start) * tile, K)}
+    if strategy == "column_wise":
+        cpr = (nbc + world_size - 1) // world_size
+        start = rank * cpr
+        end = min(start + cpr, nbc)
+        idx = np.nonzero((block_cols >= start) & (block_cols < end))[0]
+        return {"ids": idx, "rows": block_rows[idx].astype(np.int32), "cols": block_cols[idx].astype(np.int32),
+                "row_range": (0, nbr), "col_range": (start, end), "shape": (M, (end - start) * tile)}
+    if strategy == "block_wise":
+        idx = np.nonzero(np.arange(len(block_rows)) % world_size == rank)[0]
+        return {"ids": idx, "rows": block_rows[idx].astype(np.int32), "cols": block_cols[idx].astype(np.int32),
+                "row_range": (0, nbr), "col_range": (0, nbc), "shape": (M, K)}
+    raise ValueError("Unknown sharding strategy: %s" % strategy)

@@ -24,6 +24,13 @@ Fixtures (all .npz, inputs included so that the tests do not depend on RNG stabi
 
   backward_small.npz gradients of VOIDSpMMFunction (dL/dA_values per stored tile, dL/dB) for a given dL/dC
 
+  shard_small.npz    shard_void_tensor for ROW_WISE, COLUMN_WISE and BLOCK_WISE at world sizes 1, 2, 3 and 8
+                     (11 x 7 block grid: a remainder and ranks past the end): ranges, kept tiles in their
+                     kept order, rebased block rows, local shape.  The reference function computes all of
+                     that and then fails in its last statement, a VOIDTensor(...) call that omits three
+                     required fields (void/distributed.py:179-186); the fixture is made with that one
+                     constructor call given defaults for the three fields, everything before it unmodified.
+
 A fixture whose arrays come out identical to the file already present is left untouched.
 """
 import os
@@ -353,6 +360,40 @@ def main():
     save("backward_small.npz", **coo_inputs(m), b=b.detach().numpy(), grad_c=grad_c.numpy(),
          block_rows=vt.block_rows.numpy(), block_cols=vt.block_cols.numpy(), c=c.detach().numpy(),
          grad_values=vals.grad.numpy(), grad_b=b.grad.numpy())
+
+    # ---------------------------------------------------------------- shard_small
+    import void.format as ref_format
+    from void.distributed import ShardingStrategy, shard_void_tensor
+    rng = np.random.default_rng(53)
+    m = block_sparse_csr(rng, 11, 7, 0.45, M=11 * 32 - 9, K=7 * 32 - 5, empty_rows=(4,))
+    vt = void.csr_to_void(m, tile_size=32)
+    vt.values[:, 0, 0] = torch.arange(vt.n_blocks, dtype=vt.values.dtype)     # every tile carries its own position
+    real_ctor = ref_format.VOIDTensor
+
+    def ctor_with_defaults(**kw):     # the three fields the reference's call leaves out
+        kw.setdefault("morton_codes", torch.zeros(0, dtype=torch.int64))
+        kw.setdefault("nnz_original", 0)
+        kw.setdefault("density", 0.0)
+        return real_ctor(**kw)
+
+    out = {"block_rows": vt.block_rows.numpy(), "block_cols": vt.block_cols.numpy(),
+           "shape": np.asarray(vt.shape, dtype=np.int64), "worlds": np.asarray([1, 2, 3, 8], dtype=np.int64)}
+    ref_format.VOIDTensor = ctor_with_defaults
+    try:
+        for strat in (ShardingStrategy.ROW_WISE, ShardingStrategy.COLUMN_WISE, ShardingStrategy.BLOCK_WISE):
+            for world in (1, 2, 3, 8):
+                for rank in range(world):
+                    d = shard_void_tensor(vt, strat, world, rank)
+                    lt = d.local_tensor
+                    tag = "%s_w%d_r%d_" % (strat.value, world, rank)
+                    out[tag + "ids"] = lt.values[:, 0, 0].numpy().astype(np.int64)
+                    out[tag + "rows"] = lt.block_rows.numpy().astype(np.int32)
+                    out[tag + "cols"] = lt.block_cols.numpy().astype(np.int32)
+                    out[tag + "meta"] = np.asarray(list(d.local_row_range) + list(d.local_col_range) + list(lt.shape) +
+                                                   [lt.n_blocks] + list(d.global_shape), dtype=np.int64)
+    finally:
+        ref_format.VOIDTensor = real_ctor
+    save("shard_small.npz", **out)
 
 
 if __name__ == "__main__":

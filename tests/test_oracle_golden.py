@@ -243,3 +243,22 @@ def test_shard_rows_cover_and_rebase():
             assert ((local_rows >= 0) & (local_rows < max(end - start, 1))).all()
             seen.append(idx)
         assert np.array_equal(np.sort(np.concatenate(seen)), np.arange(len(g["block_rows"])))
+
+
+def test_sharding_matches_reference_output():
+    """Ranges, kept tiles (in kept order), rebased rows and local shape of all three strategies against the
+    output of the reference's own shard_void_tensor (shard_small.npz), including a remainder and ranks past
+    the end of the grid."""
+    g = load_golden("shard_small.npz")
+    shape = tuple(int(x) for x in g["shape"])
+    for strategy in ("row_wise", "column_wise", "block_wise"):
+        for world in (int(w) for w in g["worlds"]):
+            for rank in range(world):
+                tag = "%s_w%d_r%d_" % (strategy, world, rank)
+                got = vo.shard(g["block_rows"], g["block_cols"], shape, world, rank, strategy)
+                meta = [int(x) for x in g[tag + "meta"]]
+                assert np.array_equal(got["ids"], g[tag + "ids"]), tag
+                assert np.array_equal(got["rows"], g[tag + "rows"]), tag
+                assert np.array_equal(got["cols"], g[tag + "cols"]), tag
+                assert list(got["row_range"]) + list(got["col_range"]) + list(got["shape"]) == meta[:6], tag
+                assert len(got["ids"]) == meta[6] and tuple(meta[7:9]) == shape

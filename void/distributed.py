@@ -1,0 +1,5 @@
+"""``void.distributed`` of the reference, served by ``void_b200.distributed``."""
+from void_b200.distributed import *      # noqa: F401,F403
+from void_b200 import distributed as _impl
+
+__all__ = list(getattr(_impl, "__all__", [n for n in dir(_impl) if not n.startswith("_")]))

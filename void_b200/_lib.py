@@ -14,7 +14,7 @@ from . import build as _build
 _LOCK = threading.Lock()
 _LIB = None
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 c_i32, c_i64, c_f32, c_vp, c_sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 
 # enums of include/void_b200.h
@@ -42,7 +42,7 @@ class SpmmArgs(ctypes.Structure):
         ("partials", c_vp), ("partials_bytes", c_i64), ("counters", c_vp), ("worker_partials", c_vp),
         ("status", c_vp),
         ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
-        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp), ("transposed", c_i32), ("reserved", c_i32),
+        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp), ("transposed", c_i32), ("test_hooks", c_i32),
     ]
 
 
@@ -50,6 +50,7 @@ _PROTOTYPES = {
     "void_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "void_b200_abi_version": (ctypes.c_int, []),
     "void_device_sm_count": (ctypes.c_int, []),
+    "void_launch_floor": (ctypes.c_int, [c_i32, c_i32, c_i32, c_vp]),
     "void_tile_index_ws_bytes": (c_sz, [c_i32, c_i32]),
     "void_build_tile_index": (ctypes.c_int, [c_vp, c_vp, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "void_format_ws_bytes": (c_sz, [c_i32, c_i32]),

@@ -13,6 +13,8 @@ from . import _lib
 
 TILE = 32
 PANEL = 128
+FLAG_NO_PREFETCH, FLAG_DIRECT_STORES, FLAG_A_STABLE = 1, 2, 4   # bits of void_spmm_args.flags
+FLAG_NO_EARLY_A = 1 << 30   # Python side only: never set FLAG_A_STABLE (measurements)
 
 
 def _aligned_empty(nbytes: int, device, align: int = 1024) -> torch.Tensor:
@@ -38,6 +40,17 @@ class PackedTiles:
     shape: tuple
     kind: int                  # _lib.KIND_*
     key: tuple = ()
+    ready: Optional[object] = None   # CUDA event recorded behind the kernels that wrote the arrays above
+    stable: bool = False             # that event has been seen complete
+
+    def is_stable(self) -> bool:
+        """True once the kernels that built this store are known to have finished.  A launch may then
+        read the store before it waits for the previous kernel of its stream (flag bit 2 of
+        void_spmm_args), because no kernel still in flight can be writing it.  The event is only
+        queried outside stream capture, and once it has been seen complete the answer is kept."""
+        if not self.stable and self.ready is not None and not torch.cuda.is_current_stream_capturing():
+            self.stable = bool(self.ready.query())
+        return self.stable
 
 
 def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch.Tensor, block_cols: torch.Tensor,
@@ -79,13 +92,21 @@ def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch
                        (M, K), kind)
 
 
+def _mark_ready(p: PackedTiles) -> PackedTiles:
+    if not torch.cuda.is_current_stream_capturing():
+        with torch.cuda.device(p.tiles.device):
+            p.ready = torch.cuda.Event()
+            p.ready.record(torch.cuda.current_stream(p.tiles.device))
+    return p
+
+
 def cached_pack(owner, values, scales, block_rows, block_cols, shape, kind) -> PackedTiles:
     """Packed store cached on the tensor object, rebuilt when its storage or contents change."""
     key = (kind, values.data_ptr(), values._version, None if scales is None else (scales.data_ptr(), scales._version),
            block_rows.data_ptr(), block_cols.data_ptr(), str(values.device), tuple(shape))
     p = getattr(owner, "_packed_cache", None)
     if p is None or p.key != key:
-        p = pack(values, scales, block_rows, block_cols, shape, kind)
+        p = _mark_ready(pack(values, scales, block_rows, block_cols, shape, kind))
         p.key = key
         owner._packed_cache = p
         owner._plan_cache = {}
@@ -197,7 +218,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
          b_scale: float = 1.0, bias=None, act: int = 0, acc_out=None, plan: Optional[Plan] = None,
          worker_partials=None, use_row_scale: bool = True, panels_per_item: int = 0, stages: int = 0,
          grid: int = 0, tiles_per_stage: int = 0, cta_shape: int = 0, trace=None, flags: int = 0,
-         row_bias=None, transposed: bool = False) -> torch.Tensor:
+         row_bias=None, transposed: bool = False, test_hooks: int = 0) -> torch.Tensor:
     """One launch of void_spmm_i8 / void_spmm_f8 / void_spmm_fp on the current stream of b's device.
     With ``transposed`` b is [N, K] and out is [N, M]: the product is out = b @ A^T, both used as they lie."""
     lib = _lib.load()
@@ -255,7 +276,10 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     a.trace = None if trace is None else trace.data_ptr()
     a.cta_shape = cta_shape
     a.transposed = 1 if transposed else 0
-    a.flags = flags
+    # bit 2: the packed store (and the plan, whose builder synchronises) is complete, so the kernel may
+    # read it before it waits for the previous kernel of the stream
+    a.flags = (flags & 0xffff) | (FLAG_A_STABLE if (packed.is_stable() and not (flags & FLAG_NO_EARLY_A)) else 0)
+    a.test_hooks = test_hooks
     with torch.cuda.device(dev):
         if es > 1:
             _lib.check(lib.void_spmm_fp(ctypes.byref(a), packed.kind, _lib.stream_ptr(dev)), "void_spmm_fp")

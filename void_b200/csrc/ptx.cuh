@@ -46,21 +46,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wall-clock limit of every device-side wait.  A wait that runs out sets *abort_flag (a
-// shared-memory word every role polls) and returns false; the kernel then drains and exits
-// with an error code in its status word instead of hanging.
-constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;  // 2 s
+// Every device-side wait has a wall-clock limit.  `ctl` points at two shared-memory words every role of the
+// CTA polls: ctl[0] is the abort flag, ctl[1] the limit in milliseconds (kDefaultWaitLimitMs unless the launch
+// asked for another).  A wait that runs out sets the abort flag and returns false; the kernel then drains and
+// exits with an error code in its status word instead of hanging.
+constexpr int kDefaultWaitLimitMs = 2000;
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* ctl) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
+      if (ctl[0]) return false;
+      if (globaltimer_ns() - t0 > (uint64_t)ctl[1] * 1000000ull) {
+        ctl[0] = 1;
         return false;
       }
     }
@@ -114,6 +115,10 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // all committed groups of this thread have finished READING shared memory / have completed entirely
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Programmatic dependent launch: block until the kernel before this one in the stream has completed and its
+// writes are visible; let the kernel after this one begin its own set-up.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Linear bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16).
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(
@@ -219,6 +224,16 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
                : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// the same into sixteen consecutive elements of a register array
+__device__ __forceinline__ void tmem_ld_32x16p(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"

@@ -76,9 +76,19 @@ struct Shape {
 };
 using Wide = Shape<4, 8, 2>;
 using Slim = Shape<2, 4, 4>;
+// Shapes of the per-tile kernel, three CTAs per SM so that an epilogue thread can hold 32 raw products in
+// registers next to its running sums: four epilogue warps with all 32 accumulator columns each, or eight
+// with 16 each (two tiles per round trip to tensor memory).
+// (The register file is split over the four schedulers of an SM, so what a thread may use follows from the
+// warps per scheduler: 28 warps -> 72 registers, 24 or 21 -> 80, 30 -> 64.)
+using Slim3 = Shape<2, 4, 3>;
+using Drain8 = Shape<1, 8, 3>;
+using Slim1 = Shape<1, 4, 4>;
+constexpr int kDefaultDrainShape = 2;   // cta_shape the one-panel per-tile kernel runs with by default
 
 // device status codes (written to the status word)
 constexpr int kStatusTimeout = 1;
+constexpr int kStatusBadPlan = 2;   // a split row of the plan points outside the scratch the caller provided
 
 struct SpmmParams {
   const uint8_t* tiles;
@@ -102,7 +112,7 @@ struct SpmmParams {
   int32_t* counters;
   int32_t* worker_partials;
   int32_t* status;
-  unsigned long long* trace;  // debugging aid: 64 timestamps per CTA, or null
+  unsigned long long* trace;  // diagnostic instantiations only: 64 timestamps per CTA
   int np;       // panels per work item
   int group;    // tiles per ring stage
   int stages;   // ring depth
@@ -111,13 +121,23 @@ struct SpmmParams {
   int tma_store;  // 16-bit outputs leave through a staging tile in shared memory and a tiled TMA store
   int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
   int n_items;  // without a plan: nbr * n_chunks
+  int a_stable;   // A's packed arrays and the plan were complete before the stream's kernels in flight started:
+                  // they may be read before the wait on the previous kernel
+  int ctr_limit;  // split rows the scratch (partials, counters) has room for
+  int wait_limit_ms;  // limit of every device-side wait
+  int drop_group;     // test hook: the producers never fill the ring stage of each CTA's first group of tiles
   unsigned long long desc_hi_a;  // B panel  (instruction operand A: MN-major, 128B swizzle)
   unsigned long long desc_hi_b;  // A tile   (instruction operand B: K-major, no swizzle)
   unsigned int idesc;
 };
 
+// Time stamps exist in the diagnostic instantiations (TRACE) only; the kernels every ordinary launch runs
+// are compiled without them.
+template <bool TRACE>
 __device__ __forceinline__ void stamp(const SpmmParams& p, int slot) {
-  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + slot] = globaltimer_ns();
+  if constexpr (TRACE) {
+    if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + slot] = globaltimer_ns();
+  }
 }
 
 struct Seg {
@@ -248,7 +268,7 @@ __device__ __forceinline__ void finish8(const OutDesc& o, int row, int n, int m0
 // Fast epilogue of sixteen raw accumulators of output column n (tile rows m0 .. m0 + 15) straight to C
 // (no raw-accumulator dump, no split row), stores specialised per output type.
 template <int KIND>
-__device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+__device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m0, const uint32_t* r,
                                          float row_scale, float cs, float bias) {
   if (n >= o.N) return;
   float v[16];
@@ -294,7 +314,7 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
 // Sixteen finished 16-bit values of output column n into the staging tile [32 m][128 n] in shared memory
 // (stage_col points at element [0][n - n0]); same arithmetic as finish16.
 template <int KIND>
-__device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+__device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n, int m0, const uint32_t* r,
                                                float row_scale, float cs, float bias, uint16_t* stage_col) {
   float v[16];
 #pragma unroll
@@ -330,7 +350,7 @@ __device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n,
 // columns m0 .. m0 + 15 of it, so the values leave in 16-byte stores.  bias_n is the bias of this n, the
 // per-m bias (o.row_bias) is the same for every thread of the warp.
 template <int KIND>
-__device__ __forceinline__ void finish16_tr(const OutDesc& o, int row, int n, int m0, const uint32_t (&r)[16],
+__device__ __forceinline__ void finish16_tr(const OutDesc& o, int row, int n, int m0, const uint32_t* r,
                                             float row_scale, float cs, float bias_n) {
   if (n >= o.N) return;
   const int c0 = row * kTile + m0;   // first output column (a row index of A)
@@ -409,10 +429,19 @@ __device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
 
 // Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
 // consumes them; group g uses ring stage g % stages and belongs to warp g % C::PW.
-template <class C, int ES, bool TR = false>
+//
+// The wait on the previous kernel of the stream sits where the first read of data that kernel may
+// have produced is.  When the caller vouches for A (p.a_stable: the packed tiles, their index arrays
+// and the plan were complete before the kernels now in flight started) the warp reads the index,
+// claims its first ring stage and starts the bulk copy of that stage's tiles BEFORE the wait, while the
+// previous kernel is still draining; only the panels of B - typically that kernel's output - are
+// requested after it.
+template <class C, int ES, bool TR, bool TRACE>
 __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtensorMap* tmap, PipeBars* bars,
-                                              uint32_t ring_base, uint32_t stage_bytes, volatile int* abort_flag,
+                                              uint32_t ring_base, uint32_t stage_bytes, volatile int* ctl,
                                               int lane, int pw) {
+  bool waited = p.a_stable == 0;
+  if (waited) grid_dependency_wait();
   int begin, end, step;
   seg_range(p, begin, end, step);
   const int G = p.group;
@@ -442,10 +471,12 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
       if (kn < ngroups && lane < G && s.t0 + kn * G + lane < s.t1) col_next = __ldg(p.tile_cols + s.t0 + kn * G + lane);
       const uint32_t full = smem_u32(&bars->full[stage]);
       const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
+      // test hook: the first group of the CTA is never delivered, so the consumer's bounded wait runs out
+      const bool drop = p.drop_group != 0 && gi == 0;
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag) ? 1 : 0;
-        if (ok) {
+        ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, ctl) ? 1 : 0;
+        if (ok && !drop) {
           mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
           bulk_load(sbase + tile_off<ES>(p, 0), p.tiles + (size_t)t * (kTileBytes * ES),
                     (uint32_t)gcnt * (kTileBytes * ES), full);
@@ -453,7 +484,11 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
-      if (lane < gcnt) {
+      if (!waited) {  // B may be the output of the previous kernel
+        grid_dependency_wait();
+        waited = true;
+      }
+      if (lane < gcnt && !drop) {
         if (TR) {
           // B stored transposed ([N, K], k contiguous): one box of 128 rows of n x 32 k per panel
           for (int q = 0; q < npan; ++q)
@@ -467,11 +502,12 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
                         n0 + q * (kPanelN / ES), col * kTile, full);
         }
       }
-      if (lane == 0 && p.trace != nullptr && i == begin && k < 16) stamp(p, 32 + k);
+      if (TRACE && lane == 0 && i == begin && k < 16) stamp<TRACE>(p, 32 + k);
       col = col_next;
     }
     g += ngroups;
   }
+  if (!waited) grid_dependency_wait();
 }
 
 // L2 prefetch of everything the CTA's first work item will stream: its packed tiles and the B panels of
@@ -520,16 +556,17 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, ui
   else mma_f16(d, a, b, idesc, acc);
 }
 
-template <class C, int ES>
+// Barriers, tensor memory and the launch of the next kernel's set-up.  Nothing here touches global memory,
+// so all of it overlaps the tail of the previous kernel of the stream (programmatic dependent launch);
+// every role then waits for that kernel where it first needs data the kernel may have written.
+template <class C, int ES, bool TRACE>
 __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtensorMap* tmap, PipeBars& bars,
-                                               uint32_t* tmem_base_s, int* abort_s, int n_acc, uint32_t tmem_cols) {
+                                               uint32_t* tmem_base_s, int* ctl_s, int n_acc, uint32_t tmem_cols) {
   const int warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) stamp(p, 62);
-  // without a plan the first item is known from the block index alone: its lines are requested
-  // while the previous kernel of the stream may still be running
-  if (warp == C::EPI0 && p.prefetch) prefetch_first_item<ES>(p, tmap, threadIdx.x & 31);
+  if (threadIdx.x == 0) stamp<TRACE>(p, 62);
   if (threadIdx.x == 0) {
-    *abort_s = 0;
+    ctl_s[0] = 0;
+    ctl_s[1] = p.wait_limit_ms;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&bars.full[s]), 1);
       mbar_init(smem_u32(&bars.empty[s]), 1);
@@ -545,27 +582,21 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
     tmem_alloc(smem_u32(tmem_base_s), tmem_cols);
     tmem_relinquish();
   }
-  // Programmatic dependent launch: the next kernel in the stream may start its own set-up while
-  // this one runs; nothing above touched global memory, everything below may, so wait here until
-  // the kernel before this one has completed and its writes are visible.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (threadIdx.x == 0) stamp(p, 63);
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (threadIdx.x == 0) stamp(p, 0);
+  grid_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (threadIdx.x == 0) stamp(p, 1);
+  if (threadIdx.x == 0) stamp<TRACE>(p, 1);
 }
 
-template <class C>
-__device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abort_s, uint32_t tmem_base,
+template <class C, bool TRACE>
+__device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* ctl_s, uint32_t tmem_base,
                                                   uint32_t tmem_cols) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (threadIdx.x == 0) stamp(p, 7);
-  if (*abort_s) {
+  if (threadIdx.x == 0) stamp<TRACE>(p, 7);
+  if (ctl_s[0]) {
     // let copies that may still be in flight land before shared memory is given back
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -579,14 +610,21 @@ __device__ __forceinline__ void pipeline_teardown(const SpmmParams& p, int* abor
 // ------------------------------------------------------------------------------------------
 // Row-accumulate kernel.
 // ------------------------------------------------------------------------------------------
-template <int KIND, class C, bool TR = false>
+// All COLS accumulator columns of one epilogue warp, requested together (no wait).
+template <int COLS>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[COLS]) {
+#pragma unroll
+  for (int c = 0; c < COLS; c += 16) tmem_ld_32x16p(taddr + (uint32_t)c, &r[c]);
+}
+
+template <int KIND, class C, bool TR = false, bool TRACE = false>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel(const __grid_constant__ CUtensorMap tmap_b,
                                                                const __grid_constant__ CUtensorMap tmap_c,
                                                                const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ int ctl_s[2];   // abort flag, wait limit in ms
   __shared__ int last_s;
   __shared__ int ok_s[2];
 
@@ -598,17 +636,19 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const uint32_t acc_cols = (uint32_t)p.np * 32u;  // TMEM columns of one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
-  volatile int* abort_flag = &abort_s;
+  volatile int* ctl = ctl_s;
 
   if (threadIdx.x == 0) last_s = 0;
-  pipeline_setup<C, ES>(p, &tmap_b, bars, &tmem_base_s, &abort_s, 2, tmem_cols);
+  pipeline_setup<C, ES, TRACE>(p, &tmap_b, bars, &tmem_base_s, ctl_s, 2, tmem_cols);
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
-    producer_loop<C, ES, TR>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
-    if (warp == 0 && lane == 0) stamp(p, 2);
+    producer_loop<C, ES, TR, TRACE>(p, &tmap_b, &bars, ring_base, stage_bytes, ctl, lane, warp);
+    if (warp == 0 && lane == 0) stamp<TRACE>(p, 2);
   } else if (warp == C::MMA) {
     if (lane == 0) {
+      // This thread reads the index of A and the plan only; everything else reaches it through the ring.
+      if (!p.a_stable) grid_dependency_wait();
       // Everything an MMA needs is kept in registers and advanced by constants: this thread runs
       // alone on its scheduler, so every dependent instruction between two MMAs costs its full
       // latency.
@@ -635,7 +675,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (i + step < end) seg_next = load_seg(p, i + step);
         const int npan = panels_in_chunk(p, s.chunk);
         const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
-        ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, abort_flag);
+        ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * acc_cols;
@@ -643,10 +683,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         int gidx = 0;
         for (int t = s.t0; t < s.t1; t += G, ++gidx) {
           const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-          if (p.trace != nullptr && i == begin && gidx < 8) stamp(p, 48 + gidx);
-          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
+          if (TRACE && i == begin && gidx < 8) stamp<TRACE>(p, 48 + gidx);
+          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, ctl);
           if (!ok) break;
-          if (p.trace != nullptr && i == begin && gidx < 16) stamp(p, 16 + gidx);
+          if (TRACE && i == begin && gidx < 16) stamp<TRACE>(p, 16 + gidx);
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
           uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
@@ -672,9 +712,9 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (!ok) break;
         if (s.t1 > s.t0) tc_commit(smem_u32(&bars.acc_full[buf]));
         else mbar_arrive(smem_u32(&bars.acc_full[buf]));
-        if (i == begin) stamp(p, 3);
+        if (i == begin) stamp<TRACE>(p, 3);
       }
-      stamp(p, 4);
+      stamp<TRACE>(p, 4);
     }
     __syncwarp();
   } else {
@@ -690,6 +730,11 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     const uint32_t stage_u32 = ring_base + (uint32_t)p.stages * stage_bytes;
     uint16_t* stage_tile = reinterpret_cast<uint16_t*>(smem_raw + (stage_u32 - smem_u32(smem_raw)));
     bool store_pending = false;
+    // hints for the first work item travel while the previous kernel of the stream drains; then this
+    // role waits for it: the column scales and biases it reads and the C it writes may be that kernel's
+    if (warp == C::EPI0 && p.prefetch) prefetch_first_item<ES>(p, &tmap_b, lane);
+    grid_dependency_wait();
+    if (epi_tid == 0) stamp<TRACE>(p, 0);
     int begin, end, step;
     seg_range(p, begin, end, step);
     uint32_t it = 0;
@@ -709,123 +754,91 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (p.col_scale != nullptr) cs = __ldg(p.col_scale + n_base) * p.b_scale;
         if (p.bias != nullptr) bias = __ldg(p.bias + n_base);
       }
+      // a split row whose scratch index lies outside what the caller provided is skipped and reported
+      const bool bad_split = s.nseg > 1 && (s.ctr < 0 || s.ctr >= p.ctr_limit);
+      if (bad_split && epi_tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusBadPlan);
       // one thread waits, the named barrier hands its verdict to all epilogue warps, so that they
       // leave the loop together if the wait gave up
-      if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, abort_flag) ? 1 : 0;
+      if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, ctl) ? 1 : 0;
       asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
       if (!ok_s[it & 1u]) break;
-      if (epi_tid == 0 && i == begin) stamp(p, 5);
-      if (epi_tid == 0) stamp(p, 8);
+      if (epi_tid == 0 && i == begin) stamp<TRACE>(p, 5);
+      if (epi_tid == 0) stamp<TRACE>(p, 8);
       tc_fence_after();
       const bool fast = s.nseg == 1 && od.acc_out == nullptr && p.worker_partials == nullptr;
 #pragma unroll 1
       for (int q = 0; q < npan; ++q) {
         const int n = n_base + q * kPanelN;
-        if (!TR && p.tma_store && fast) {
-          // 16-bit outputs: the 32 x 128 result tile is put together in shared memory and leaves in one
-          // tiled store; the copy engine clips it at the edges of C.  The staging tile is free again once
-          // the previous store has read it.
-          if (store_pending) {
-            if (epi_tid == 0) bulk_wait_read();
-            asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
-          }
-          float csq = p.b_scale, biasq = 0.0f;
-          if (n < p.N) {
-            if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
-            if (p.bias != nullptr) biasq = __ldg(p.bias + n);
-          }
-#pragma unroll
-          for (int c = 0; c < C::COLS; c += 16) {
-            uint32_t r[16];
-            if (has) {
-              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int k = 0; k < 16; ++k) r[k] = 0u;
-            }
-            if (q == npan - 1 && c + 16 >= C::COLS) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-            }
-            finish16_stage<KIND>(od, s.row, n, m_first + c, r, rs, csq, biasq, stage_tile + quad * 32 + lane);
-          }
-          fence_proxy_async_smem();
-          asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
-          if (epi_tid == 0) {
-            tma_store_2d(&tmap_c, stage_u32, (s.chunk * p.np + q) * kPanelN, s.row * kTile);
-            bulk_commit();
-          }
-          store_pending = true;
-          continue;
-        }
-        if (TR) {  // transposed output: this thread's 32 values are contiguous in its output row n
-          float csq = p.b_scale, biasq = 0.0f;
-          if (n < p.N) {
-            if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
-            if (p.bias != nullptr) biasq = __ldg(p.bias + n);
-          }
-#pragma unroll
-          for (int c = 0; c < C::COLS; c += 16) {
-            uint32_t r[16];
-            if (has) {
-              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int k = 0; k < 16; ++k) r[k] = 0u;
-            }
-            if (q == npan - 1 && c + 16 >= C::COLS) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-            }
-            finish16_tr<KIND>(od, s.row, n, m_first + c, r, rs, csq, biasq);
-          }
-          continue;
-        }
-        float cs_next = p.b_scale, bias_next = 0.0f;
-        if (q + 1 < npan && n + kPanelN < p.N) {
-          if (p.col_scale != nullptr) cs_next = __ldg(p.col_scale + n + kPanelN) * p.b_scale;
-          if (p.bias != nullptr) bias_next = __ldg(p.bias + n + kPanelN);
-        }
+        const uint32_t acc_addr = tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first);
         if (fast) {
-#pragma unroll
-          for (int c = 0; c < C::COLS; c += 16) {
-            uint32_t r[16];
-            if (has) {
-              tmem_ld_32x16(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m_first + c), r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int k = 0; k < 16; ++k) r[k] = 0u;
+          // All of this warp's columns of the panel are requested at once and awaited once; the
+          // accumulator buffer goes back to the MMA warp as soon as the values sit in registers.
+          float csq = cs, biasq = bias;
+          if (q > 0) {
+            csq = p.b_scale; biasq = 0.0f;
+            if (n < p.N) {
+              if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+              if (p.bias != nullptr) biasq = __ldg(p.bias + n);
             }
-            if (epi_tid == 0 && q == 0) stamp(p, 9 + (c >> 4) * 2);
-            if (q == npan - 1 && c + 16 >= C::COLS) {  // this warp is done with the accumulator buffer
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-            }
-            finish16<KIND>(od, s.row, n, m_first + c, r, rs, cs, bias);
-            if (epi_tid == 0 && q == 0) stamp(p, 10 + (c >> 4) * 2);
           }
-          cs = cs_next;
-          bias = bias_next;
+          uint32_t r[C::COLS];
+          if (has) {
+            tmem_ld_cols<C::COLS>(acc_addr, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int k = 0; k < C::COLS; ++k) r[k] = 0u;
+          }
+          if (epi_tid == 0 && q == 0) stamp<TRACE>(p, 9);
+          if (q == npan - 1) {  // this warp is done with the accumulator buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+          }
+          if (!TR && p.tma_store) {
+            // 16-bit outputs: the 32 x 128 result tile is put together in shared memory and leaves in one
+            // tiled store; the copy engine clips it at the edges of C.  The staging tile is free again once
+            // the previous store has read it.
+            if (store_pending) {
+              if (epi_tid == 0) bulk_wait_read();
+              asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
+            }
+#pragma unroll
+            for (int c = 0; c < C::COLS; c += 16)
+              finish16_stage<KIND>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, stage_tile + quad * 32 + lane);
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
+            if (epi_tid == 0) {
+              tma_store_2d(&tmap_c, stage_u32, (s.chunk * p.np + q) * kPanelN, s.row * kTile);
+              bulk_commit();
+            }
+            store_pending = true;
+          } else {
+#pragma unroll
+            for (int c = 0; c < C::COLS; c += 16) {
+              if (TR) finish16_tr<KIND>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq);
+              else finish16<KIND>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq);
+            }
+          }
+          if (epi_tid == 0 && q == 0) stamp<TRACE>(p, 10);
           continue;
+        }
+        float csq = p.b_scale, biasq = 0.0f;
+        if (n < p.N) {
+          if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+          if (p.bias != nullptr) biasq = __ldg(p.bias + n);
         }
 #pragma unroll 1
         for (int c = 0; c < C::COLS; c += 8) {
           const int m0 = m_first + c;
           uint32_t r[8];
           if (has) {
-            tmem_ld_32x8(tmem_base + lane_sel + buf * acc_cols + (uint32_t)(q * 32 + m0), r);
+            tmem_ld_32x8(acc_addr + (uint32_t)c, r);
             tmem_ld_wait();
           } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) r[k] = 0u;
           }
-          if (epi_tid == 0 && q == 0) stamp(p, 9 + (c >> 3) * 2);
           if (q == npan - 1 && c + 8 >= C::COLS) {  // this warp is done with the accumulator buffer
             tc_fence_before();
             __syncwarp();
@@ -837,9 +850,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             for (int k = 0; k < 8; ++k) w[(size_t)k * p.N] = r[k];
           }
           if (s.nseg == 1) {
-            finish8<KIND>(od, s.row, n, m0, r, rs, cs, bias);
-            if (epi_tid == 0 && q == 0) stamp(p, 10 + (c >> 3) * 2);
-          } else {
+            finish8<KIND>(od, s.row, n, m0, r, rs, csq, biasq);
+          } else if (!bad_split) {
             // partial sum of a split row: added into the row's int32 accumulator in global memory
             // (integer adds commute, so the total does not depend on which CTA comes first)
             int32_t* dst = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
@@ -851,15 +863,13 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             }
           }
         }
-        cs = cs_next;
-        bias = bias_next;
       }
-      if (s.nseg > 1) {
+      if (s.nseg > 1 && !bad_split) {
         // the CTA that arrives last reads the completed sums back and finishes the row
-        if (epi_tid == 0) stamp(p, 12);
+        if (epi_tid == 0) stamp<TRACE>(p, 12);
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
-        if (epi_tid == 0) stamp(p, 13);
+        if (epi_tid == 0) stamp<TRACE>(p, 13);
         if (epi_tid == 0) {
           const int old = atomicAdd(p.counters + s.ctr, 1);
           const int last = (old == s.nseg - 1) ? 1 : 0;
@@ -869,8 +879,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         const int last = last_s;
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
-        if (epi_tid == 0) stamp(p, 14);
-        if (epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
+        if (epi_tid == 0) stamp<TRACE>(p, 14);
+        if (TRACE && epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
         if (last) {
           __threadfence();
 #pragma unroll 1
@@ -905,22 +915,24 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         }
       }
     }
-    if (store_pending && epi_tid == 0) bulk_wait_all();  // the last tile has left shared memory and reached C
-    if (epi_tid == 0) stamp(p, 6);
+    // the staging tile must have been read before shared memory is given back; the writes themselves
+    // complete with the kernel
+    if (store_pending && epi_tid == 0) bulk_wait_read();
+    if (epi_tid == 0) stamp<TRACE>(p, 6);
   }
-  pipeline_teardown<C>(p, &abort_s, tmem_base, tmem_cols);
+  pipeline_teardown<C, TRACE>(p, ctl_s, tmem_base, tmem_cols);
 }
 
 // ------------------------------------------------------------------------------------------
 // Per-tile drain kernel: every tile's product is scaled by that tile's scale.
 // ------------------------------------------------------------------------------------------
-template <int KIND, int NP, class C>
+template <int KIND, int NP, class C, bool TRACE = false>
 __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) spmm_drain_kernel(const __grid_constant__ CUtensorMap tmap_b,
                                                               const __grid_constant__ SpmmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ int ctl_s[2];   // abort flag, wait limit in ms
 
   // Tensor memory is cut into slot groups: one group receives the products of the tiles of one ring
   // stage (up to p.group tiles, NP panels each), so that MMA warp and epilogue hand over once per
@@ -928,6 +940,11 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
   constexpr uint32_t kTileCols = NP * 32;   // TMEM columns of one tile's product
   const uint32_t kTmemCols = (uint32_t)p.tmem_cols;
   constexpr int CW = C::COLS;
+  // Products are read back in batches of 32 registers per thread with ONE wait per batch: both halves of a
+  // tile for a warp that owns all 32 accumulator columns, the halves of two tiles for a warp that owns 16.
+  // A read of tensor memory is a round trip of a few hundred cycles whatever its width, and the fold that
+  // follows depends on it, so the number of round trips per tile is what this role's speed hangs on.
+  constexpr int TPW = 32 / CW;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -935,16 +952,17 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
   const uint32_t stage_bytes = (uint32_t)(p.group * (NP * kPanelBytes + kTileBytes));
   const uint32_t group_cols = (uint32_t)p.group * kTileCols;
   const int n_slots = (int)(kTmemCols / group_cols);   // >= 2: checked at launch
-  volatile int* abort_flag = &abort_s;
+  volatile int* ctl = ctl_s;
 
-  pipeline_setup<C, 1>(p, &tmap_b, bars, &tmem_base_s, &abort_s, n_slots, kTmemCols);
+  pipeline_setup<C, 1, TRACE>(p, &tmap_b, bars, &tmem_base_s, ctl_s, n_slots, kTmemCols);
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp < C::PW) {
-    producer_loop<C, 1>(p, &tmap_b, &bars, ring_base, stage_bytes, abort_flag, lane, warp);
-    if (warp == 0 && lane == 0) stamp(p, 2);
+    producer_loop<C, 1, false, TRACE>(p, &tmap_b, &bars, ring_base, stage_bytes, ctl, lane, warp);
+    if (warp == 0 && lane == 0) stamp<TRACE>(p, 2);
   } else if (warp == C::MMA) {
     if (lane == 0) {
+      if (!p.a_stable) grid_dependency_wait();
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
       const int G = p.group, S = p.stages;
@@ -964,9 +982,9 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
         const int npan = panels_in_chunk(p, s.chunk);
         for (int t = s.t0; t < s.t1; t += G) {
           const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
+          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, ctl);
           if (!ok) break;
-          ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, abort_flag);
+          ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, ctl);
           if (!ok) break;
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
@@ -991,7 +1009,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
           if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
       }
-      stamp(p, 4);
+      stamp<TRACE>(p, 4);
     }
     __syncwarp();
   } else {
@@ -999,8 +1017,9 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
     const int half = (warp - C::EPI0) >> 2;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
     const int m_first = half * CW;
-    const OutDesc od = out_desc(p);
     const int G = p.group;
+    if (warp == C::EPI0 && p.prefetch) prefetch_first_item<1>(p, &tmap_b, lane);
+    grid_dependency_wait();
     int begin, end, step;
     seg_range(p, begin, end, step);
     int slot = 0;
@@ -1022,31 +1041,39 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
         // scale of lane j's tile, fetched before the products are ready
         const float my_ts = (lane < gcnt) ? __ldg(p.tile_scales + t + lane) : 0.0f;
         int ok = 1;
-        if (lane == 0) ok = mbar_wait(smem_u32(&bars.acc_full[slot]), sphase, abort_flag) ? 1 : 0;
+        if (lane == 0) ok = mbar_wait(smem_u32(&bars.acc_full[slot]), sphase, ctl) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) { alive = false; break; }
         tc_fence_after();
-        for (int j = 0; j < gcnt; ++j) {
-          const float ts = __shfl_sync(0xffffffffu, my_ts, j);
-          const uint32_t tile_addr = tmem_base + lane_sel + (uint32_t)slot * group_cols + (uint32_t)j * kTileCols +
-                                     (uint32_t)m_first;
+        const uint32_t slot_addr = tmem_base + lane_sel + (uint32_t)slot * group_cols + (uint32_t)m_first;
+        for (int j = 0; j < gcnt; j += TPW) {
 #pragma unroll
           for (int q = 0; q < NP; ++q) {
             if (q < npan) {
+              uint32_t r[TPW][CW];
 #pragma unroll
-              for (int c = 0; c < CW; c += 16) {
-                uint32_t r[16];
-                tmem_ld_32x16(tile_addr + (uint32_t)(q * 32 + c), r);
-                tmem_ld_wait();
-                if (j == gcnt - 1 && q == npan - 1 && c + 16 >= CW) {  // this warp has read the whole slot group
-                  tc_fence_before();
-                  __syncwarp();
-                  if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
+              for (int u = 0; u < TPW; ++u) {
+                if (j + u < gcnt) {
+#pragma unroll
+                  for (int c = 0; c < CW; c += 16)
+                    tmem_ld_32x16p(slot_addr + (uint32_t)(j + u) * kTileCols + (uint32_t)(q * 32 + c), &r[u][c]);
                 }
+              }
+              tmem_ld_wait();
+              if (j + TPW >= gcnt && q == npan - 1) {  // this warp has read the whole slot group
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[slot]));
+              }
 #pragma unroll
-                for (int m = 0; m < 16; ++m) {
-                  const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[m]) : __uint_as_float(r[m]);
-                  acc[q][c + m] = fmaf(ts, x, acc[q][c + m]);
+              for (int u = 0; u < TPW; ++u) {
+                if (j + u < gcnt) {   // tiles are folded in their stored order, one after the other
+                  const float ts = __shfl_sync(0xffffffffu, my_ts, j + u);
+#pragma unroll
+                  for (int m = 0; m < CW; ++m) {
+                    const float x = (KIND == VOID_KIND_I8) ? __int2float_rn((int)r[u][m]) : __uint_as_float(r[u][m]);
+                    acc[q][m] = fmaf(ts, x, acc[q][m]);
+                  }
                 }
               }
             }
@@ -1055,6 +1082,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
         if (++slot == n_slots) { slot = 0; sphase ^= 1u; }
       }
       if (!alive) break;
+      const OutDesc od = out_desc(p);   // read here, not before the loop: registers are what this role is short of
       const int n_base = s.chunk * NP * kPanelN + quad * 32 + lane;
 #pragma unroll
       for (int q = 0; q < NP; ++q) {
@@ -1079,9 +1107,9 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
         }
       }
     }
-    if (threadIdx.x == 32 * C::EPI0) stamp(p, 6);
+    if (threadIdx.x == 32 * C::EPI0) stamp<TRACE>(p, 6);
   }
-  pipeline_teardown<C>(p, &abort_s, tmem_base, kTmemCols);
+  pipeline_teardown<C, TRACE>(p, ctl_s, tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1167,6 +1195,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (a->act < VOID_ACT_NONE || a->act > VOID_ACT_SILU) return VOID_ERR_BAD_ARG;
   if (a->scale_mode != VOID_SCALE_ROW_MEAN && a->scale_mode != VOID_SCALE_PER_TILE) return VOID_ERR_BAD_ARG;
   if (a->scale_mode == VOID_SCALE_PER_TILE && a->nnz > 0 && a->tile_scales == nullptr) return VOID_ERR_BAD_ARG;
+  if (a->segs != nullptr && a->partials_bytes > 0 && (a->partials == nullptr || a->counters == nullptr)) return VOID_ERR_BAD_ARG;
   if ((long long)a->nbr * kTile < a->M) return VOID_ERR_SHAPE;
   const bool tr = a->transposed != 0;
   if (a->transposed != 0 && a->transposed != 1) return VOID_ERR_BAD_ARG;
@@ -1206,20 +1235,22 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   // per item; the wide one for the per-tile kernel and for four-panel items (TMEM: 2 x np x 32
   // columns per row-accumulate CTA, 512 per SM)
   int shape = a->cta_shape;
-  if (shape < 0 || shape > 2) return VOID_ERR_BAD_ARG;
+  if (shape < 0 || shape > 5) return VOID_ERR_BAD_ARG;
   if (tr && np > 2) return VOID_ERR_BAD_ARG;
   if (tr && shape == 1) return VOID_ERR_BAD_ARG;  // built for the slim shape only
-  if (shape == 0) shape = ((!drain && np <= 2) || (drain && np == 1)) ? 2 : 1;
+  if (shape == 0) shape = (!drain && np <= 2) ? 2 : ((drain && np == 1) ? kDefaultDrainShape : 1);
   if (shape == 2 && (np > 2 || (drain && np > 1))) return VOID_ERR_BAD_ARG;
+  if (shape >= 3 && (!drain || np != 1 || tr)) return VOID_ERR_BAD_ARG;  // shapes of the per-tile kernel
   const bool slim = (shape == 2);
-  const int producer_warps = slim ? Slim::PW : Wide::PW;
-  const int ctas_per_sm = slim ? Slim::CTAS_PER_SM : ((np == 4) ? 1 : Wide::CTAS_PER_SM);
+  const int producer_warps = (shape == 1) ? Wide::PW : ((shape >= 4) ? 1 : Slim::PW);
+  const int ctas_per_sm = (slim || shape == 5) ? 4 : (shape >= 3 ? 3 : ((np == 4) ? 1 : Wide::CTAS_PER_SM));
   int group = a->tiles_per_stage;  // 0 = default
   if (group == 0) group = (np == 1) ? 4 : 2;  // few, large ring stages beat a deep ring of small ones
   if (a->tiles_per_stage == 0 && floating) group = (es == 2 && np == 1) ? 2 : 1;
   if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
-  if (drain && slim && a->tiles_per_stage == 0) group = 2;
-  const int drain_tmem = 512 / ctas_per_sm;
+  if (drain && np == 1 && shape != 1 && a->tiles_per_stage == 0) group = 2;
+  int drain_tmem = 32;   // the largest power of two that lets ctas_per_sm CTAs share the SM's 512 columns
+  while (drain_tmem * 2 * ctas_per_sm <= 512) drain_tmem *= 2;
   if (drain && group * np * 32 * 2 > drain_tmem) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
   const int stage_bytes = group * (np * kPanelBytes + kTileBytes) * es;
   int stages = a->stages;
@@ -1278,6 +1309,20 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.prefetch = ((a->flags & 1) || tr) ? 0 : 1;
   p.tma_store = tma_store ? 1 : 0;
   p.n_items = a->nbr * n_chunks;
+  p.a_stable = (a->flags & 4) ? 1 : 0;
+  // room of the split-row scratch, in rows: the kernel refuses segments whose counter index lies beyond it
+  p.ctr_limit = 0;
+  if (a->segs != nullptr && a->partials != nullptr && a->counters != nullptr && a->partials_bytes > 0) {
+    const long long rows = a->partials_bytes / ((long long)np * kPanelN * kTile * (long long)sizeof(int32_t));
+    p.ctr_limit = rows > 0x7fffffffll ? 0x7fffffff : (int)rows;
+  }
+  // test hooks (args->test_hooks): bits 0..15 = limit of every device-side wait in milliseconds (0: the
+  // default), bit 16 = the producers never deliver the first group of tiles of each CTA
+  p.wait_limit_ms = (a->test_hooks & 0xffff) ? (a->test_hooks & 0xffff) : kDefaultWaitLimitMs;
+  p.drop_group = (a->test_hooks >> 16) & 1;
+  if (a->trace != nullptr && !((kind == VOID_KIND_I8 && !drain && slim && !tr) ||
+                               (kind == VOID_KIND_F8E4M3 && drain && np == 1 && shape >= 2)))
+    return VOID_ERR_BAD_ARG;   // time stamps exist in the diagnostic instantiations only
 
   // Operand descriptors.  Packed tile (instruction operand B, K-major, no swizzle): 8x16-byte core
   // matrices, 128 bytes between the two k-halves (leading offset), 256 bytes between 8-row groups
@@ -1386,6 +1431,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (ensure_smem((const void*)KERNEL, smem_bytes)) return VOID_ERR_CUDA;                   \
     launch_pdl(KERNEL, grid, SHAPE::THREADS, smem_bytes, stream, tmap, tmap_c, p);            \
   } while (0)
+  const bool traced = a->trace != nullptr;
   if (tr) {
     if (kind == VOID_KIND_TF32) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_TF32, Slim, true>), Slim);
     else if (kind == VOID_KIND_I8) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim, true>), Slim);
@@ -1400,19 +1446,30 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     }
   } else if (!drain) {
     if (kind == VOID_KIND_I8) {
-      if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
+      if (slim && traced) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim, false, true>), Slim);
+      else if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Slim>), Slim);
       else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_I8, Wide>), Wide);
     } else {
       if (slim) VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Slim>), Slim);
       else VB_LAUNCH_ROWACC((spmm_rowacc_kernel<VOID_KIND_F8E4M3, Wide>), Wide);
     }
   } else if (kind == VOID_KIND_I8) {
-    if (np == 1 && slim) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim>), Slim);
+    if (np == 1 && shape == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim>), Slim);
+    else if (np == 1 && shape == 3) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim3>), Slim3);
+    else if (np == 1 && shape == 4) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Drain8>), Drain8);
+    else if (np == 1 && shape == 5) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Slim1>), Slim1);
     else if (np == 1) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 1, Wide>), Wide);
     else if (np == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 2, Wide>), Wide);
     else VB_LAUNCH((spmm_drain_kernel<VOID_KIND_I8, 4, Wide>), Wide);
   } else {
-    if (np == 1 && slim) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim>), Slim);
+    if (np == 1 && shape == 2 && traced) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim, true>), Slim);
+    else if (np == 1 && shape == 3 && traced) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim3, true>), Slim3);
+    else if (np == 1 && shape == 4 && traced) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Drain8, true>), Drain8);
+    else if (np == 1 && shape == 5 && traced) return VOID_ERR_BAD_ARG;
+    else if (np == 1 && shape == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim>), Slim);
+    else if (np == 1 && shape == 3) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim3>), Slim3);
+    else if (np == 1 && shape == 4) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Drain8>), Drain8);
+    else if (np == 1 && shape == 5) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Slim1>), Slim1);
     else if (np == 1) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 1, Wide>), Wide);
     else if (np == 2) VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 2, Wide>), Wide);
     else VB_LAUNCH((spmm_drain_kernel<VOID_KIND_F8E4M3, 4, Wide>), Wide);
@@ -1460,7 +1517,9 @@ static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_split_rows,
   if (st != VOID_OK) return st;
   void_spmm_args b = *a;
   b.partials = base;
-  b.partials_bytes = (int64_t)kStaticPartialsBytes;
+  // the room the kernel may use is what this call clears: a segment of the plan whose counter index is
+  // n_split_rows or more is skipped and reported through the status word instead of touching the rest
+  b.partials_bytes = (int64_t)((size_t)n_split_rows * acc_bytes);
   b.counters = reinterpret_cast<int32_t*>(base + kStaticPartialsBytes);
   // The array keeps whatever the previous call left.  Row accumulators and counters must start at
   // zero (a launch that ran to the end leaves them so, a launch that gave up may not), so the part
@@ -1473,9 +1532,22 @@ static int spmm_i8_static_scratch(const void_spmm_args* a, int32_t n_split_rows,
   return spmm_launch(&b, VOID_KIND_I8, stream);
 }
 
+// A kernel that does nothing but take part in programmatic dependent launch the way the SpMM kernels do.
+__global__ void floor_kernel() {
+  grid_launch_dependents();
+  grid_dependency_wait();
+}
+
 }  // namespace vb
 
 extern "C" {
+
+int void_launch_floor(int32_t grid, int32_t threads, int32_t smem_bytes, void_stream_t stream) {
+  if (grid < 1 || threads < 32 || threads > 1024 || smem_bytes < 0) return VOID_ERR_BAD_ARG;
+  if (vb::ensure_smem((const void*)vb::floor_kernel, smem_bytes)) return VOID_ERR_CUDA;
+  vb::launch_pdl(vb::floor_kernel, grid, threads, smem_bytes, reinterpret_cast<cudaStream_t>(stream));
+  return cudaGetLastError() == cudaSuccess ? VOID_OK : VOID_ERR_CUDA;
+}
 
 int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_split_rows, void_stream_t stream) {
   return vb::spmm_i8_static_scratch(args, n_split_rows, reinterpret_cast<cudaStream_t>(stream));

@@ -73,16 +73,17 @@ __global__ void __launch_bounds__(kThreads, 2) tile_grad_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   __shared__ Bars bars;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ int abort_s[2];   // abort flag, wait limit in ms
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  volatile int* abort_flag = &abort_s;
+  volatile int* abort_flag = abort_s;
   constexpr uint32_t kTmemCols = 64;  // two accumulators of 32 columns
 
   if (threadIdx.x == 0) {
-    abort_s = 0;
+    abort_s[0] = 0;
+    abort_s[1] = kDefaultWaitLimitMs;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bars.full[s]), 1);
       mbar_init(smem_u32(&bars.empty[s]), 1);
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2) tile_grad_kernel(const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (abort_s) {
+  if (abort_s[0]) {
     const uint64_t t0 = globaltimer_ns();  // let copies still in flight land before shared memory is given back
     while (globaltimer_ns() - t0 < 200000ull) {
     }

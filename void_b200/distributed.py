@@ -14,7 +14,18 @@ reference's return value); gather_output=False returns the local row shard.
 
 The reference's shard_void_tensor raises TypeError (its VOIDTensor(...) call omits required
 fields, :179-186); this one fills them in and also accepts Int8VOIDTensor / FP8VOIDTensor.
-Only ROW_WISE is built: COLUMN_WISE / BLOCK_WISE need a reduction and are outside this path.
+
+COLUMN_WISE (:127-137) and BLOCK_WISE (:139-145) give every rank tiles of ALL tile rows, so the
+per-rank products are partial sums of the whole C and the reference adds them with an all_reduce of
+the full [M, N] matrix (:252-267).  Here the sum is part of the INT8 SpMM kernel itself
+(fused_reduce_spmm): output tile rows are owned by ranks (the ROW_WISE ranges), every rank adds its
+int32 partial tiles straight into the owner's accumulator through peer memory (NVLink), bumps the
+owner's arrival counter, and whichever rank arrives last reads the finished sums back, dequantises
+and writes the owner's rows of C - a reduce-scatter without a separate collective and without any
+kernel waiting for another GPU.  Integer adds commute, so the result does not depend on arrival order.
+
+nnz-balanced ROW_WISE ranges (balance="nnz") cut the tile rows where the running tile count crosses
+k/world of the total instead of at equal row counts; the reference's ranges stay the default.
 """
 from dataclasses import dataclass
 from enum import Enum
@@ -36,7 +47,10 @@ class ShardingStrategy(Enum):
 
 @dataclass
 class DistributedVOIDTensor:
-    """Local shard plus sharding metadata (void/distributed.py:17-62)."""
+    """Local shard plus sharding metadata (void/distributed.py:17-62).  The fields after
+    local_col_range are additions: row_ranges lists every rank's tile-row range when it is not the
+    reference's equal split (balance="nnz"); global_row_scale carries the mean tile scale of every
+    tile row of the WHOLE tensor, which the INT8 epilogue needs when a rank holds only part of a row."""
     local_tensor: Union[VOIDTensor, Int8VOIDTensor, FP8VOIDTensor]
     strategy: ShardingStrategy
     world_size: int
@@ -44,6 +58,8 @@ class DistributedVOIDTensor:
     global_shape: Tuple[int, int]
     local_row_range: Tuple[int, int]
     local_col_range: Tuple[int, int]
+    row_ranges: Optional[Tuple[Tuple[int, int], ...]] = None
+    global_row_scale: Optional[torch.Tensor] = None
 
     @property
     def device(self) -> torch.device:
@@ -55,7 +71,17 @@ class DistributedVOIDTensor:
 
     def to(self, device) -> "DistributedVOIDTensor":
         return DistributedVOIDTensor(self.local_tensor.to(device), self.strategy, self.world_size, self.rank,
-                                     self.global_shape, self.local_row_range, self.local_col_range)
+                                     self.global_shape, self.local_row_range, self.local_col_range, self.row_ranges,
+                                     None if self.global_row_scale is None else self.global_row_scale.to(device))
+
+    def owner_ranges(self) -> Tuple[Tuple[int, int], ...]:
+        """Tile rows [start, end) of C each rank owns: this tensor's row ranges for ROW_WISE, the
+        reference's equal split of the rows for the strategies that reduce."""
+        if self.row_ranges is not None:
+            return self.row_ranges
+        tile_m = self.local_tensor.tile_size[0]
+        nbr = (self.global_shape[0] + tile_m - 1) // tile_m
+        return tuple(row_range(nbr, self.world_size, r) for r in range(self.world_size))
 
 
 def is_distributed() -> bool:
@@ -77,52 +103,119 @@ def row_range(n_block_rows: int, world_size: int, rank: int) -> Tuple[int, int]:
     return start, min(start + rows_per_rank, n_block_rows)
 
 
-def shard_void_tensor(void_tensor, strategy: ShardingStrategy = ShardingStrategy.ROW_WISE,
-                      world_size: Optional[int] = None, rank: Optional[int] = None) -> DistributedVOIDTensor:
-    """Keep this rank's tile rows of a VOIDTensor / Int8VOIDTensor / FP8VOIDTensor."""
-    if world_size is None:
-        world_size = get_world_size()
-    if rank is None:
-        rank = get_rank()
-    if strategy != ShardingStrategy.ROW_WISE:
-        if not isinstance(strategy, ShardingStrategy):
-            raise ValueError(f"Unknown sharding strategy: {strategy}")
-        raise NotImplementedError("void_b200 shards ROW_WISE only (no reduction between GPUs)")
-    n_block_rows, n_block_cols = void_tensor.block_grid
-    tile_m, tile_k = void_tensor.tile_size
-    start_row, end_row = row_range(n_block_rows, world_size, rank)
-    mask = (void_tensor.block_rows >= start_row) & (void_tensor.block_rows < end_row)
-    indices = torch.where(mask)[0]
+def balanced_row_ranges(block_rows: torch.Tensor, n_block_rows: int, world_size: int) -> Tuple[Tuple[int, int], ...]:
+    """Contiguous tile-row ranges that minimise the largest number of stored tiles any rank gets (the
+    bottleneck partition: binary search on the capacity, greedy fill).  Equal row counts (the reference's
+    split) leave ranks idle when the tiles per row are far from uniform."""
+    counts = torch.bincount(block_rows.to(torch.int64).cpu(), minlength=n_block_rows)[:n_block_rows].tolist()
+
+    def cuts_for(capacity):
+        cuts, load = [0], 0
+        for r, c in enumerate(counts):
+            if load + c > capacity and load > 0:
+                cuts.append(r)
+                load = 0
+            load += c
+        return cuts
+
+    lo, hi = max(counts + [0]), max(sum(counts), 1)
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if len(cuts_for(mid)) <= world_size:
+            hi = mid
+        else:
+            lo = mid + 1
+    cuts = cuts_for(lo)
+    cuts += [n_block_rows] * (world_size + 1 - len(cuts))      # ranks past the last cut own nothing
+    return tuple((cuts[k], cuts[k + 1]) for k in range(world_size))
+
+
+def _take(void_tensor, indices, local_rows, local_cols, local_shape, grid_cells):
+    """The tiles ``indices`` of a VOIDTensor / Int8VOIDTensor / FP8VOIDTensor as a tensor of the same class."""
     n_local = int(indices.numel())
-    local_rows = (void_tensor.block_rows[indices] - start_row).to(torch.int32)
-    local_cols = void_tensor.block_cols[indices]
-    local_shape = ((end_row - start_row) * tile_m, void_tensor.shape[1])
-    grid_cells = max((end_row - start_row) * n_block_cols, 1)
+    tile_m, tile_k = void_tensor.tile_size
     if isinstance(void_tensor, Int8VOIDTensor):
-        local = Int8VOIDTensor(values=void_tensor.values[indices], scales=void_tensor.scales[indices],
-                               zero_points=void_tensor.zero_points[indices], block_rows=local_rows,
-                               block_cols=local_cols, shape=local_shape, tile_size=void_tensor.tile_size,
-                               n_blocks=n_local, config=void_tensor.config)
-    elif isinstance(void_tensor, FP8VOIDTensor):
+        return Int8VOIDTensor(values=void_tensor.values[indices], scales=void_tensor.scales[indices],
+                              zero_points=void_tensor.zero_points[indices], block_rows=local_rows,
+                              block_cols=local_cols, shape=local_shape, tile_size=void_tensor.tile_size,
+                              n_blocks=n_local, config=void_tensor.config)
+    if isinstance(void_tensor, FP8VOIDTensor):
         s = void_tensor.scaling_info
         per_tile = s.scale.dim() == 1 and s.scale.numel() == void_tensor.n_blocks
         pick = (lambda t: t[indices]) if per_tile else (lambda t: t)
         info = FP8ScalingInfo(scale=pick(s.scale), scale_inv=pick(s.scale_inv), amax=pick(s.amax),
                               amax_history=pick(s.amax_history), config=s.config)
-        local = FP8VOIDTensor(values_fp8=void_tensor.values_fp8[indices], scaling_info=info, block_rows=local_rows,
-                              block_cols=local_cols, morton_codes=void_tensor.morton_codes[indices], shape=local_shape,
-                              tile_size=void_tensor.tile_size, nnz_original=n_local * tile_m * tile_k,
-                              n_blocks=n_local, density=n_local / grid_cells)
+        return FP8VOIDTensor(values_fp8=void_tensor.values_fp8[indices], scaling_info=info, block_rows=local_rows,
+                             block_cols=local_cols, morton_codes=void_tensor.morton_codes[indices], shape=local_shape,
+                             tile_size=void_tensor.tile_size, nnz_original=n_local * tile_m * tile_k,
+                             n_blocks=n_local, density=n_local / grid_cells)
+    values = void_tensor.values[indices]
+    return VOIDTensor(values=values, block_rows=local_rows, block_cols=local_cols,
+                      morton_codes=void_tensor.morton_codes[indices], shape=local_shape,
+                      tile_size=void_tensor.tile_size,
+                      nnz_original=int(torch.count_nonzero(values).item()) if n_local else 0,
+                      n_blocks=n_local, density=n_local / grid_cells, dtype=void_tensor.dtype)
+
+
+def shard_void_tensor(void_tensor, strategy: ShardingStrategy = ShardingStrategy.ROW_WISE,
+                      world_size: Optional[int] = None, rank: Optional[int] = None, *,
+                      balance: str = "rows") -> DistributedVOIDTensor:
+    """Keep this rank's tiles of a VOIDTensor / Int8VOIDTensor / FP8VOIDTensor (void/distributed.py:84-196).
+
+    ROW_WISE: tile rows [rank * ceil(nbr / world), ...) with block_rows rebased (:115-125, :159-161);
+    balance="nnz" replaces the equal split by balanced_row_ranges.  COLUMN_WISE: block columns
+    [rank * ceil(nbc / world), ...), block_cols NOT rebased, local shape shrunk to the range
+    (:127-137, :173-176).  BLOCK_WISE: stored tile i goes to rank i % world (:139-145).
+    Kept tiles stay in their stored (Morton) order.
+    """
+    if world_size is None:
+        world_size = get_world_size()
+    if rank is None:
+        rank = get_rank()
+    if not isinstance(strategy, ShardingStrategy):
+        raise ValueError(f"Unknown sharding strategy: {strategy}")
+    if balance not in ("rows", "nnz"):
+        raise ValueError("balance must be 'rows' or 'nnz'")
+    n_block_rows, n_block_cols = void_tensor.block_grid
+    tile_m, tile_k = void_tensor.tile_size
+    row_ranges = None
+    global_row_scale = None
+    if strategy == ShardingStrategy.ROW_WISE:
+        if balance == "nnz":
+            row_ranges = balanced_row_ranges(void_tensor.block_rows, n_block_rows, world_size)
+            start_row, end_row = row_ranges[rank]
+        else:
+            start_row, end_row = row_range(n_block_rows, world_size, rank)
+        mask = (void_tensor.block_rows >= start_row) & (void_tensor.block_rows < end_row)
+        local_row_range, local_col_range = (start_row, end_row), (0, n_block_cols)
+        local_shape = ((end_row - start_row) * tile_m, void_tensor.shape[1])
+    elif strategy == ShardingStrategy.COLUMN_WISE:
+        cols_per_rank = (n_block_cols + world_size - 1) // world_size
+        start_col = min(rank * cols_per_rank, n_block_cols)
+        end_col = min(start_col + cols_per_rank, n_block_cols)
+        mask = (void_tensor.block_cols >= start_col) & (void_tensor.block_cols < end_col)
+        local_row_range, local_col_range = (0, n_block_rows), (start_col, end_col)
+        local_shape = (void_tensor.shape[0], (end_col - start_col) * tile_k)
     else:
-        values = void_tensor.values[indices]
-        local = VOIDTensor(values=values, block_rows=local_rows, block_cols=local_cols,
-                           morton_codes=void_tensor.morton_codes[indices], shape=local_shape,
-                           tile_size=void_tensor.tile_size,
-                           nnz_original=int(torch.count_nonzero(values).item()) if n_local else 0,
-                           n_blocks=n_local, density=n_local / grid_cells, dtype=void_tensor.dtype)
+        positions = torch.arange(void_tensor.n_blocks, device=void_tensor.block_rows.device)
+        mask = (positions % world_size) == rank
+        local_row_range, local_col_range = (0, n_block_rows), (0, n_block_cols)
+        local_shape = tuple(void_tensor.shape)
+    indices = torch.where(mask)[0]
+    local_rows = void_tensor.block_rows[indices].to(torch.int32)
+    if strategy == ShardingStrategy.ROW_WISE:
+        local_rows = (void_tensor.block_rows[indices] - local_row_range[0]).to(torch.int32)
+    local_cols = void_tensor.block_cols[indices]
+    cells = max((local_row_range[1] - local_row_range[0]) * (local_col_range[1] - local_col_range[0]), 1)
+    local = _take(void_tensor, indices, local_rows, local_cols, local_shape, cells)
+    if strategy != ShardingStrategy.ROW_WISE and isinstance(void_tensor, Int8VOIDTensor) and void_tensor.values.is_cuda:
+        # INT8 semantic: a tile row's accumulator is scaled by the mean of ALL of the row's tile scales
+        # (void/int_quant.py:516-526); a rank that holds part of the row needs the whole row's mean
+        global_row_scale = void_tensor.packed().row_scale[:n_block_rows].clone()
     return DistributedVOIDTensor(local_tensor=local, strategy=strategy, world_size=world_size, rank=rank,
-                                 global_shape=void_tensor.shape, local_row_range=(start_row, end_row),
-                                 local_col_range=(0, n_block_cols))
+                                 global_shape=tuple(void_tensor.shape), local_row_range=local_row_range,
+                                 local_col_range=local_col_range, row_ranges=row_ranges,
+                                 global_row_scale=global_row_scale)
 
 
 def broadcast_b(b: torch.Tensor, src: int = 0, group=None, scales: Optional[torch.Tensor] = None):

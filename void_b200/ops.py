@@ -41,7 +41,7 @@ def packed_fp(a: VOIDTensor, kind: int) -> _spmm.PackedTiles:
         return hit
     vals = a.values if a.values.dtype == _KIND_DTYPE[kind] else a.values.to(_KIND_DTYPE[kind])
     row_ptr, block_indices = a.get_row_block_info()
-    p = _spmm.pack(vals, None, a.block_rows, a.block_cols, a.shape, kind, row_ptr, block_indices)
+    p = _spmm._mark_ready(_spmm.pack(vals, None, a.block_rows, a.block_cols, a.shape, kind, row_ptr, block_indices))
     p.key = key
     cache[kind] = p
     a._plan_cache = {}
@@ -66,6 +66,9 @@ def void_spmm(a: VOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         raise _lib.VoidB200Error("void_spmm: B must be float32, float16 or bfloat16, got %s" % b.dtype)
     if out is None:
         out = torch.empty(M, N, dtype=b.dtype, device=b.device)
+    if a.n_blocks == 0 and activation == 0 and bias is None and row_bias is None and plan is None \
+            and acc_out is None and worker_partials is None:
+        return out.zero_()      # nothing stored: zeros, whatever the tile size (void/ops.py:169-173)
     kind = product_kind(a, b)
     packed = packed_fp(a, kind)
     if b.dtype != _KIND_DTYPE[kind]:
