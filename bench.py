@@ -37,10 +37,55 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "block_sparse_spmm_tops_nonzero_tiles"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (C stays in the write-back L2 during a launch, so less than the algorithmic bytes)
-MEASURED_TRAFFIC = {"headline": 3.87e6, "fp8": 3.88e6, "powerlaw": 13.6e6, "fp32": 15.1e6}
+# ncu summary of the dominant kernel per workload: roofline.traffic is read from it (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch), it is not measured by this run
+PROFILE_OF = {"headline": "spmm_rowacc_int8_headline.md", "fp8": "spmm_rowacc_fp8_headline.md",
+              "powerlaw": "spmm_rowacc_int8_powerlaw_streamk.md", "fp32": "spmm_rowacc_tf32_headline.md",
+              "sharded": "spmm_rowacc_int8_sharded65536.md"}
 L2_BYTES = 126 * 1024 * 1024
+STRONG_WORKLOAD = "uniform65536_bs95_n1024"
+
+
+def profiled_traffic(workload):
+    """(bytes per launch, source) from the committed ncu summary of the workload's kernel, or (None, None)."""
+    import re
+    name = PROFILE_OF.get(workload)
+    path = os.path.join(ROOT, "profiles", name) if name else None
+    if not path or not os.path.exists(path):
+        return None, None
+    text = open(path).read()
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    total, seen = 0.0, set()
+    for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        m = re.search(r"^\s*" + re.escape(key) + r"\s+([0-9.]+)\s+(byte|Kbyte|Mbyte|Gbyte)\b", text, re.M)
+        if m:
+            total += float(m.group(1)) * unit[m.group(2)]
+            seen.add(key)
+    if len(seen) < 2:
+        return None, None
+    return total, "profiles/%s (ncu capture of one launch, static)" % name
+
+
+def workload_config(args, world):
+    """What both arms print as ``config``: a description of the workload that does not depend on what ran it.
+    nnz_tiles is the realised tile count of the first input copy of one GPU (seed 0)."""
+    import numpy as np
+    from void_b200 import workloads
+    if args.workload == "powerlaw":
+        nnz = int(workloads.zipf_mask(512, 512, 1.5, 512, 15.36, 0).sum())
+        cfg = {"workload": "zipf16384_n256_streamk_gelu", "M_per_gpu": 16384, "K": 16384, "N": 256, "out_dtype": "bfloat16"}
+    elif args.workload == "sharded":
+        nnz = int(round(2048 * 2048 * 0.05))
+        cfg = {"workload": STRONG_WORKLOAD + "_rowshards", "M_per_gpu": 65536 // world, "K": 65536, "N": 1024,
+               "out_dtype": "float16"}
+    else:
+        nnz = int(workloads.uniform_mask(128, 128, args.sparsity, 0).sum())
+        out = {"fp32": "float32"}.get(args.workload, "float16")
+        cfg = {"workload": "uniform4096_bs%02d_n512%s" % (round(args.sparsity * 100), "" if world == 1 else "_x%d_rowshards" % world),
+               "M_per_gpu": 4096, "K": 4096, "N": 512, "out_dtype": out}
+    cfg.update({"tile": 32, "nnz_tiles": nnz, "l2": "rotating_inputs", "parallelism": "row_shards_x%d" % world,
+                "strong_scaling_workload": STRONG_WORKLOAD if world > 1 else None})
+    return cfg
 
 
 def parse_args():
@@ -142,22 +187,27 @@ def cpu_reference_arm(args, rank, world):
     import torch
     from oracle import void_oracle as vo
     cfg, run, cores = cpu_workload(args, np, torch, vo)
-    for _ in range(min(args.warmup, 1)):
+    t_w = time.perf_counter()
+    for w in range(args.warmup):
         run()
+        if time.perf_counter() - t_w > 30.0:      # the requested warm-up, unless the host is far too slow for it
+            break
     t0 = time.perf_counter()
     n = 0
-    budget = 120.0
+    budget = 150.0
     while n < args.steps and (time.perf_counter() - t0) < budget:
         run()
         n += 1
     dt = (time.perf_counter() - t0) / n
     tops = cfg["ops"] / dt / 1e12
     line = {
-        "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus, "steps": n, "warmup": min(args.warmup, 1),
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": cfg["dtype"], "data": "synthetic", "impl": "reference", "config": cfg["config"],
+        "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus, "steps": n, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if args.workload == "sharded" else "weak",
+        "vs_baseline": None,
+        "dtype": cfg["dtype"], "data": "synthetic", "impl": "reference", "config": workload_config(args, world),
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
-                         "sample": "whole %s workload per step, %d steps, %s" % (cfg["config"]["workload"], n, cfg["how"])},
+                         "sample": "one GPU's share of the workload (%s, %d tiles) per step, %d steps, %s"
+                                   % (cfg["config"]["workload"], cfg["config"]["nnz_tiles"], n, cfg["how"])},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -386,22 +436,43 @@ def main():
                 for i in range(K_steps):
                     step(i)
 
+    # One pass = exactly K steps.  A pass of the default K lasts a fraction of a millisecond, too short for
+    # the clock sampler and for a stable mean, so the pass is repeated back to back until the timed region
+    # covers at least MIN_TIMED_MS; every pass is bracketed by its own pair of events on the launching stream.
+    MIN_TIMED_MS = 50.0
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.window[0] = time.perf_counter()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
-        e0.record(stream)
+        p0.record(stream)
     run_timed()
     with torch.cuda.stream(stream):
-        e1.record(stream)
+        p1.record(stream)
+    torch.cuda.synchronize()
+    probe_ms = max(p0.elapsed_time(p1), 1e-3)
+    passes = int(min(max(1, -(-MIN_TIMED_MS // probe_ms)), 4000))
+    if world > 1:
+        agreed = torch.tensor([passes], dtype=torch.int64, device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+        passes = int(agreed.item())
+        dist.barrier()
+    torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(passes + 1)]
+    sampler.window[0] = time.perf_counter()
+    with torch.cuda.stream(stream):
+        marks[0].record(stream)
+    for r in range(passes):
+        run_timed()
+        with torch.cuda.stream(stream):
+            marks[r + 1].record(stream)
     torch.cuda.synchronize()
     sampler.window[1] = time.perf_counter()
     if world > 1:
         dist.barrier()
-    ms_total = e0.elapsed_time(e1)
+    pass_ms = [marks[r].elapsed_time(marks[r + 1]) for r in range(passes)]
+    ms_total = marks[0].elapsed_time(marks[passes]) / passes      # mean time of one pass of K steps
+    ms_min = min(pass_ms)
     _lib.check_device_status(dev)
 
     # ---- end to end through the public operator with host buffers: every step copies its B (and
@@ -471,6 +542,7 @@ def main():
     # The same three steps in flight with each slot's step (copy-in, operator, copy-out) captured once as
     # a CUDA graph and replayed on the slot's own stream: the work per step is unchanged, the Python
     # launch path (about ten API calls per step) leaves the timed loop.
+    E2E_WHAT = "; B arrives already quantised (8-bit B and its column scales are the step's input), A is resident"
     e2e_mode = "host wall clock, %d steps in flight (copy-in / operator / copy-out streams)" % DEPTH
     slot_graphs = None
     # (not for the planned launch: its split-row scratch belongs to one launch at a time, and the
@@ -558,13 +630,14 @@ def main():
         dist.all_reduce(ts, op=dist.ReduceOp.MAX)
         first_step = {"broadcast_then_spmm_ms": float(ts[0]), "overlapped_panels_ms": float(ts[1]), "panel_cols": 256}
 
+    strong = None
     # ---- aggregate over ranks: max time, summed work
-    t = torch.tensor([ms_total, e2e_ms, e2e_serial_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, e2e_ms, e2e_serial_ms, ms_min], dtype=torch.float64, device=dev)
     work = torch.tensor([ops_per_step_local, float(np.mean(nnz_local))], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(work, op=dist.ReduceOp.SUM)
-    ms_total, e2e_ms, e2e_serial_ms = (float(x) for x in t.tolist())
+    ms_total, e2e_ms, e2e_serial_ms, ms_min = (float(x) for x in t.tolist())
     ops_per_step, nnz_total = (float(x) for x in work.tolist())
 
     if rank == 0:
@@ -574,14 +647,10 @@ def main():
         achieved = bytes_per_step / (ms_per_step * 1e-3) / 1e9
         ops_per_byte = ops_per_step_local / bytes_per_step
         clocks = sampler.summary()
-        name = info["name"] or ("%s_x%d_rowshards" % (sets[0][0].__class__.__name__, world))
-        if args.workload in ("headline", "fp8", "fp32", "fp16"):
-            name = "uniform4096_bs%02d_n512%s" % (round(args.sparsity * 100), "" if world == 1 else "_x%d_rowshards" % world)
-        elif args.workload == "powerlaw":
-            name = "zipf16384_n256_streamk_gelu"
         # ops/byte above (dense 8-bit peak / HBM peak) makes the tensor cores the bound; the 8-bit peak is
         # taken as twice the measured bf16 GEMM rate (the ratio of the nominal dense figures)
         # (fp16: the bf16 rate itself; fp32 operands as TF32: half of it)
+        traffic, traffic_source = profiled_traffic(args.workload) if world == 1 else (None, None)
         peak_tops = {"tf32": 0.5, "f16": 1.0}.get(kind, 2.0) * peaks["bf16_tflops"]
         tensor_bound = ops_per_byte > peak_tops * 1e12 / (peaks["hbm_gbs"] * 1e9)
         local_tops = ops_per_step_local / (ms_per_step * 1e-3) / 1e12
@@ -590,7 +659,7 @@ def main():
                     "peak": peak_tops if tensor_bound else peaks["hbm_gbs"],
                     "unit": "TOPS" if tensor_bound else "GB/s",
                     "frac": (local_tops / peak_tops) if tensor_bound else achieved / peaks["hbm_gbs"],
-                    "traffic": MEASURED_TRAFFIC.get(args.workload if world == 1 else None),
+                    "traffic": traffic, "traffic_source": traffic_source,
                     "peak_source": peaks["source"] + (" (2 x bf16 GEMM)" if tensor_bound else " (copy)"),
                     "algorithmic_bytes_per_launch": bytes_per_step, "algorithmic_ops_per_launch": ops_per_step_local,
                     "ops_per_byte": ops_per_byte, "hbm_gbs_achieved": achieved, "kernel_us": ms_per_step * 1e3}
@@ -600,19 +669,20 @@ def main():
             "scaling": "strong" if args.workload == "sharded" else "weak",
             "vs_baseline": vs_published(args, world, ms_per_step),
             "dtype": kind, "data": "synthetic",
-            "config": {"workload": name, "M_per_gpu": M_local, "K": K, "N": N, "tile": 32,
-                       "nnz_tiles": nnz_total, "out_dtype": str(sets[0][3].dtype).replace("torch.", ""),
-                       "l2": "rotating_inputs", "input_copies": len(sets), "cuda_graph": not args.no_graph,
-                       "b_broadcast_ms": bcast_ms, "first_step": first_step, "parallelism": "row_shards_x%d" % world},
+            "config": workload_config(args, world),
+            "run": {"nnz_tiles_mean_all_gpus": nnz_total, "input_copies": len(sets), "cuda_graph": not args.no_graph,
+                    "timed_launches": passes * K_steps, "passes_of_k_steps": passes, "timed_ms": ms_total * passes,
+                    "ms_per_step_min_pass": ms_min / K_steps, "b_broadcast_ms": bcast_ms, "first_step": first_step},
+            "strong_scaling": strong,
             "roofline": roofline,
             "e2e": {"value": ops_per_step / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h_b.numel() + h_s.numel() * 4),
                     "d2h_bytes_per_step": int(h_c.numel() * h_c.element_size()),
-                    "mode": e2e_mode,
+                    "mode": e2e_mode + E2E_WHAT,
                     "one_step_at_a_time_ms": e2e_serial_ms,
                     "one_step_at_a_time_value": ops_per_step / (e2e_serial_ms * 1e-3) / 1e12,
                     "results_identical_across_slots": e2e_check},
-            "gpu_launches": K_steps,
+            "gpu_launches": passes * K_steps,
             "clocks": clocks,
         }
         if not args.no_cpu_baseline and world == 1 and args.workload != "sharded":

@@ -72,6 +72,9 @@ VOID_API int void_b200_abi_version(void);
  * void/int_quant.py:158-175 and void/fp8.py:712-720): row_ptr[nbr+1] = exclusive prefix sum
  * of tiles per tile row, block_indices[nnz] = argsort of (block_row * nbc + block_col).
  * Keys are unique, so the result is bit-exact with the reference's torch.argsort.
+ * The tile list is not trusted: coordinates outside [0, nbr) x [0, nbc) are skipped and a coordinate
+ * pair that occurs twice is counted once, so a bad list shows as row_ptr[nbr] < nnz (block_indices
+ * then still holds valid positions only, but not a permutation) - check it before using the index.
  * ws: caller workspace of void_tile_index_ws_bytes(nbr, nbc) bytes (a bitmap of the block
  * grid plus per-row counters).
  * ------------------------------------------------------------------------------------- */
@@ -132,6 +135,21 @@ VOID_API int void_pack_tiles(const void* values, const float* scales, int64_t n_
                     const int32_t* row_ptr, int64_t nnz, int32_t nbr, void* packed,
                     int32_t* tile_cols, float* tile_scales, float* row_scale,
                     void_stream_t stream);
+
+/* FP8 tiles with their scales folded in (void_spmm_f8 with VOID_SCALE_ROW_MEAN and args->tile_terms = terms).
+ * The reference multiplies every tile by its own scale before it is added to the row's sum
+ * (void/fp8.py:638-659); the tensor cores cannot scale per tile, and reading every tile's product back to do
+ * it in registers is what made the FP8 product slower than the INT8 one.  Here each element
+ * a * scale_tile / R_row, R_row = the largest tile scale of the tile row, is stored as a sum of `terms`
+ * (2 or 3) E4M3 numbers (nearest value, then the nearest value of the remainder): 8 significant bits with two
+ * terms, 12 with three - the reference's own tl.dot rounds this operand to TF32's 11.  Packed tile j holds
+ * its terms one after the other, (j * terms + k) * 1024; row_scale[r] receives R_row, which the epilogue
+ * applies; tile_cols / tile_scales as in void_pack_tiles.  packed: nnz * terms * 1024 bytes, 1024-byte aligned. */
+VOID_API int void_pack_tiles_f8_split(const void* values, const float* scales, int64_t n_scales,
+                                      const int32_t* block_rows, const int32_t* block_cols,
+                                      const int32_t* block_indices, const int32_t* row_ptr, int64_t nnz,
+                                      int32_t nbr, int32_t terms, void* packed, int32_t* tile_cols,
+                                      float* tile_scales, float* row_scale, void_stream_t stream);
 
 /* Same gather for floating-point tiles (VOIDTensor.values, void/format.py:66): elem_bytes = 2
  * (fp16 / bf16) or 4 (fp32).  A packed tile takes 1024 * elem_bytes bytes and is stored as
@@ -269,7 +287,7 @@ typedef struct void_spmm_args {
   int32_t panels_per_item; /* 128-column panels of B per work item: 1, 2 or 4            */
   int32_t stages;          /* shared-memory ring depth                                   */
   int32_t grid;            /* CTAs to launch without a plan                              */
-  int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1, 2, 4 or 8      */
+  int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1 ... 8         */
   /* diagnostics: NULL for every ordinary launch.  Not NULL selects a separately compiled diagnostic kernel
    * (slim INT8 row-accumulate or one-panel FP8 per-tile only, else VOID_ERR_BAD_ARG) that writes 64
    * uint64 nanosecond timestamps per launched CTA; the ordinary kernels contain none of that code.   */
@@ -277,8 +295,8 @@ typedef struct void_spmm_args {
   int32_t cta_shape;       /* 0 default; 1 wide CTAs (13 warps, 2 per SM); 2 slim (7 warps, 4 per SM);
                               per-tile kernel with one panel only: 3 = 7 warps, 3 per SM; 4 = 10 warps, 3 per SM;
                               5 = 6 warps, 4 per SM */
-  int32_t flags;           /* bit 0: no L2 prefetch of the first work item; bit 1: no staged TMA store of
-                              16-bit outputs (direct stores);
+  int32_t flags;           /* bit 1: no staged TMA store of 16-bit outputs (direct stores); bit 4: staged 16-bit
+                              outputs leave in one store per result tile instead of one per epilogue warp;
                               bit 2: the caller vouches that the packed A (tiles, tile_cols, tile_scales,
                               row_ptr, row_scale) and the plan were completely written before any kernel
                               still in flight on the stream started - they are then read BEFORE the wait on
@@ -301,6 +319,29 @@ typedef struct void_spmm_args {
    * delivered to the consumer, so that its wait runs out, the launch gives up in an orderly way and the
    * status word reads 1 - used to test that path without any faulting or unbounded wait.            */
   int32_t test_hooks;
+  /* 0 or 1: one packed tile per stored tile.  2 or 3 (void_spmm_f8, VOID_SCALE_ROW_MEAN only): tiles packed by
+   * void_pack_tiles_f8_split - every stored tile is a sum of that many E4M3 terms, 1024 bytes each, stored
+   * one after the other; the kernel multiplies all terms by the same panel of B.                        */
+  int32_t tile_terms;
+  int32_t reserved;
+  /* Reduction across GPUs inside the kernel (0: off).  Replaces the all_reduce of the full [M, N] result that
+   * the reference runs after the local products of COLUMN_WISE / BLOCK_WISE shards, void/distributed.py:252-267.
+   * With n_peers = world size, every segment of the plan is one rank's part of a tile row (nseg = number of ranks
+   * that contribute, slot0 = the rank that OWNS the row, counter = the row's index in the owner's scratch).  The
+   * kernel adds its int32 partial tile into peer_partials[owner] with system-scope atomic adds (NVLink when the
+   * owner is another GPU), bumps peer_counters[owner][counter], and whichever rank arrives last reads the sums
+   * back, dequantises and writes the owner's rows of C through peer_out[owner] - a pointer to the owner's C
+   * shard moved back by the owner's first row, so that the GLOBAL tile row indexes it.  All three arrays hold
+   * one pointer per rank, valid on this GPU (the rank's own buffers for its own index); partials_bytes is the
+   * size of each rank's accumulator array.  No kernel waits for another GPU; the caller orders consecutive
+   * launches (every rank's launch i must have finished before any rank's launch i+1 adds into the same
+   * scratch, e.g. by a small collective on the stream).  Row-accumulate kernel only, not with transposed,
+   * acc_out or worker_partials.                                                                        */
+  int32_t n_peers;
+  int32_t reserved2;
+  void* peer_partials[8];
+  int32_t* peer_counters[8];
+  void* peer_out[8];
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

@@ -58,8 +58,8 @@ def test_fp8_and_float_tensors_shard_without_crashing():
     parts = [void.distributed_void_spmm(void.shard_void_tensor(a8, world_size=4, rank=r), b8, b_scale=bs,
                                         gather_output=False) for r in range(4)]
     assert torch.equal(torch.cat(parts), full)
-    with pytest.raises(NotImplementedError):
-        void.shard_void_tensor(w.a, void.ShardingStrategy.COLUMN_WISE, world_size=2, rank=0)
+    with pytest.raises(ValueError):
+        void.shard_void_tensor(w.a, "diagonal", world_size=2, rank=0)
 
 
 def test_sharded_generator_matches_global_mask():

@@ -161,38 +161,59 @@ def test_linearity_and_row_permutation_properties():
     assert dense.shape == (4096, 4096)
 
 
-def test_fp8_spmm_vs_reference_fixture():
+# How far each way of applying A's per-tile scales may be from the reference's output: 0 = every tile's fp32
+# product scaled in registers (exact), 3 / 2 = scales folded into A as a sum of three / two E4M3 terms.
+FP8_TERMS_TOL = {0: 1e-5, 3: 1e-4, 2: 2e-3}
+
+
+@pytest.mark.parametrize("terms", [0, 3, 2])
+def test_fp8_spmm_vs_reference_fixture(terms):
     g = load_golden("fp8_small.npz")
     a = void.csr_to_void(coo_to_csr(g), device="cuda")
     a8 = void.void_tensor_to_fp8(a)
     b8 = torch.from_numpy(g["b_fp8"]).cuda().view(torch.float8_e4m3fn)
     bs = torch.from_numpy(g["b_scale"]).cuda()
-    c = void.void_spmm_fp8(a8, b8, torch.float32, b_scale=bs)
-    assert rel_err(_np(c), g["c_block"]) < 1e-5             # far inside the 1e-2 bar
-    c16 = void.void_spmm_fp8(a8, b8, b_scale=bs)            # default output dtype: fp16
+    tol = FP8_TERMS_TOL[terms]
+    c = void.void_spmm_fp8(a8, b8, torch.float32, b_scale=bs, scale_terms=terms)
+    assert rel_err(_np(c), g["c_block"]) < tol              # far inside the 1e-2 bar
+    c16 = void.void_spmm_fp8(a8, b8, b_scale=bs, scale_terms=terms)      # default output dtype: fp16
     assert c16.dtype == torch.float16 and rel_err(_np(c16), g["c_f16"]) < FP8_TOL
-    c_raw = void.void_spmm_fp8(a8, b8, torch.float32)       # unit B scales
-    assert rel_err(_np(c_raw), g["c_block_rawb"]) < 1e-5
-    c_fb = void.void_spmm_fp8(a8, torch.from_numpy(g["b"]).cuda(), torch.float32)   # fp32 B quantised here
-    assert rel_err(_np(c_fb), g["c_block"]) < 1e-5
+    c_raw = void.void_spmm_fp8(a8, b8, torch.float32, scale_terms=terms)       # unit B scales
+    assert rel_err(_np(c_raw), g["c_block_rawb"]) < tol
+    c_fb = void.void_spmm_fp8(a8, torch.from_numpy(g["b"]).cuda(), torch.float32, scale_terms=terms)   # fp32 B quantised here
+    assert rel_err(_np(c_fb), g["c_block"]) < tol
+    # one scale for all tiles: nothing to fold, every form is exact
     at = void.void_tensor_to_fp8(a, scale_mode="per_tensor")
-    ct = void.void_spmm_fp8(at, b8, torch.float32, b_scale=bs)
+    ct = void.void_spmm_fp8(at, b8, torch.float32, b_scale=bs, scale_terms=terms)
     assert rel_err(_np(ct), g["c_tensor"]) < 1e-5
     void.check_device_status()
 
 
+def test_fp8_default_scale_terms_follow_the_output_type():
+    g = load_golden("fp8_small.npz")
+    a8 = void.void_tensor_to_fp8(void.csr_to_void(coo_to_csr(g), device="cuda"))
+    b8 = torch.from_numpy(g["b_fp8"]).cuda().view(torch.float8_e4m3fn)
+    bs = torch.from_numpy(g["b_scale"]).cuda()
+    for dtype, terms in ((torch.float16, 2), (torch.bfloat16, 2), (torch.float32, 3)):
+        assert torch.equal(void.void_spmm_fp8(a8, b8, dtype, b_scale=bs),
+                           void.void_spmm_fp8(a8, b8, dtype, b_scale=bs, scale_terms=terms))
+    with pytest.raises(ValueError):
+        void.void_spmm_fp8(a8, b8, b_scale=bs, scale_terms=4)
+
+
+@pytest.mark.parametrize("terms", [0, 2, 3])
 @pytest.mark.parametrize("sparsity", [0.70, 0.80, 0.90, 0.95, 0.98])
-def test_fp8_spmm_sparsity_sweep_vs_oracle(sparsity):
+def test_fp8_spmm_sparsity_sweep_vs_oracle(sparsity, terms):
     w = workloads.headline(sparsity, seed=1)
     a8 = void.void_tensor_to_fp8(w.a)
     b8, bs, _ = void.quantize_cols_fp8(w.b)
-    c = void.void_spmm_fp8(a8, b8, torch.float16, b_scale=bs)
+    c = void.void_spmm_fp8(a8, b8, torch.float16, b_scale=bs, scale_terms=terms)
     void.check_device_status()
     b_deq = vo.fp8_bytes_to_float(b8.view(torch.uint8).cpu().numpy()) * _np(bs)[None, :]
     ref = vo.spmm_fp8(a8.values_fp8.view(torch.uint8).cpu().numpy(), _np(a8.scaling_info.scale),
                       _np(a8.block_rows).astype(np.int32), _np(a8.block_cols).astype(np.int32), (4096, 4096), b_deq)
     assert rel_err(_np(c), ref) < FP8_TOL
-    assert rel_err(_np(c), ref) < 2e-3                      # fp16 rounding is all that is left
+    assert rel_err(_np(c), ref) < 2e-3                      # fp16 rounding (and, for two terms, 8-bit folded scales)
     # reference's own accuracy bar for FP8 SpMM: mean relative error < 0.3 against fp32 (tests/test_fp8.py:233-238)
     dense = (w.a.to_dense() @ w.b)
     mean_rel = ((c.float() - dense).abs().mean() / dense.abs().mean()).item()

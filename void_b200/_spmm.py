@@ -13,7 +13,7 @@ from . import _lib
 
 TILE = 32
 PANEL = 128
-FLAG_NO_PREFETCH, FLAG_DIRECT_STORES, FLAG_A_STABLE = 1, 2, 4   # bits of void_spmm_args.flags
+FLAG_DIRECT_STORES, FLAG_A_STABLE, FLAG_STORE_PER_TILE = 2, 4, 16   # bits of void_spmm_args.flags
 FLAG_NO_EARLY_A = 1 << 30   # Python side only: never set FLAG_A_STABLE (measurements)
 
 
@@ -39,17 +39,13 @@ class PackedTiles:
     nnz: int
     shape: tuple
     kind: int                  # _lib.KIND_*
+    terms: int = 1             # packed tiles per stored tile (2 / 3: FP8 tiles stored as sums of E4M3 terms)
     key: tuple = ()
-    ready: Optional[object] = None   # CUDA event recorded behind the kernels that wrote the arrays above
-    stable: bool = False             # that event has been seen complete
+    stable: bool = False       # the kernels that wrote the arrays above are known to have finished
 
     def is_stable(self) -> bool:
-        """True once the kernels that built this store are known to have finished.  A launch may then
-        read the store before it waits for the previous kernel of its stream (flag bit 2 of
-        void_spmm_args), because no kernel still in flight can be writing it.  The event is only
-        queried outside stream capture, and once it has been seen complete the answer is kept."""
-        if not self.stable and self.ready is not None and not torch.cuda.is_current_stream_capturing():
-            self.stable = bool(self.ready.query())
+        """True when no kernel still in flight can be writing this store.  A launch may then read
+        the store before it waits for the previous kernel of its stream (flag bit 2 of void_spmm_args)."""
         return self.stable
 
 
@@ -92,11 +88,44 @@ def pack(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch
                        (M, K), kind)
 
 
+def pack_f8_split(values: torch.Tensor, scales: Optional[torch.Tensor], block_rows: torch.Tensor,
+                  block_cols: torch.Tensor, shape, terms: int) -> PackedTiles:
+    """Packed store of FP8 tiles with their scales folded in (void_pack_tiles_f8_split): every tile as a sum
+    of ``terms`` E4M3 tiles relative to the largest tile scale of its tile row, which lands in row_scale."""
+    from .format import build_tile_index
+    _lib.require_cuda(values, block_rows, block_cols)
+    lib = _lib.load()
+    dev = values.device
+    M, K = shape
+    nbr, nbc = (M + TILE - 1) // TILE, (K + TILE - 1) // TILE
+    nnz = values.shape[0]
+    if values.dim() != 3 or tuple(values.shape[1:]) != (TILE, TILE) or values.element_size() != 1:
+        raise _lib.VoidB200Error("void_b200 kernels need 32x32 FP8 tiles here, got %s %s" % (tuple(values.shape), values.dtype))
+    with torch.cuda.device(dev):
+        row_ptr, block_indices = build_tile_index(block_rows, block_cols, nbr, nbc)
+        vals = values.contiguous()
+        tiles = _aligned_empty(max(nnz, 1) * 1024 * terms, dev)
+        tile_cols = torch.empty(max(nnz, 1), dtype=torch.int32, device=dev)
+        tile_scales = torch.empty(max(nnz, 1), dtype=torch.float32, device=dev)
+        row_scale = torch.empty(max(nbr, 1), dtype=torch.float32, device=dev)
+        sc = None if scales is None else scales.contiguous().to(torch.float32).reshape(-1)
+        br = block_rows.contiguous().to(torch.int32)
+        bc = block_cols.contiguous().to(torch.int32)
+        _lib.check(lib.void_pack_tiles_f8_split(_lib.ptr(vals), _lib.ptr(sc), 0 if sc is None else sc.numel(), _lib.ptr(br),
+                                                _lib.ptr(bc), _lib.ptr(block_indices), _lib.ptr(row_ptr), nnz, nbr, terms,
+                                                _lib.ptr(tiles), _lib.ptr(tile_cols), _lib.ptr(tile_scales),
+                                                _lib.ptr(row_scale), _lib.stream_ptr(dev)), "void_pack_tiles_f8_split")
+    return PackedTiles(tiles, tile_cols, tile_scales, row_ptr, block_indices, row_scale, nbr, nbc, nnz, (M, K),
+                       _lib.KIND_F8E4M3, terms)
+
+
 def _mark_ready(p: PackedTiles) -> PackedTiles:
+    # Building a packed store is a one-time set-up step of a tensor (a weight): the host waits here until the
+    # store is complete, so that every later launch may read it ahead of its stream order.  Inside a stream
+    # capture nothing can be waited for; a store built there is simply never read early.
     if not torch.cuda.is_current_stream_capturing():
-        with torch.cuda.device(p.tiles.device):
-            p.ready = torch.cuda.Event()
-            p.ready.record(torch.cuda.current_stream(p.tiles.device))
+        torch.cuda.current_stream(p.tiles.device).synchronize()
+        p.stable = True
     return p
 
 
@@ -280,6 +309,7 @@ def spmm(packed: PackedTiles, b: torch.Tensor, out: torch.Tensor, *, scale_mode:
     # read it before it waits for the previous kernel of the stream
     a.flags = (flags & 0xffff) | (FLAG_A_STABLE if (packed.is_stable() and not (flags & FLAG_NO_EARLY_A)) else 0)
     a.test_hooks = test_hooks
+    a.tile_terms = packed.terms
     with torch.cuda.device(dev):
         if es > 1:
             _lib.check(lib.void_spmm_fp(ctypes.byref(a), packed.kind, _lib.stream_ptr(dev)), "void_spmm_fp")

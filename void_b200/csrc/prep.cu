@@ -43,11 +43,14 @@ __device__ void block_exclusive_scan(const int32_t* in, int32_t* out, int n) {
 }
 
 // ------------------------------------------------------------------------------ tile index
+// Coordinates outside the block grid are skipped here and in rank_tiles_kernel: the caller sees them (and
+// repeated coordinates, which set one bit twice) as row_ptr[nbr] < nnz.
 __global__ void mark_tiles_kernel(const int32_t* __restrict__ brow, const int32_t* __restrict__ bcol, int64_t nnz,
-                                  int wpr, uint32_t* __restrict__ bitmap) {
+                                  int nbr, int nbc, int wpr, uint32_t* __restrict__ bitmap) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nnz) return;
   const int r = brow[i], c = bcol[i];
+  if ((unsigned)r >= (unsigned)nbr || (unsigned)c >= (unsigned)nbc) return;
   atomicOr(bitmap + (size_t)r * wpr + (c >> 5), 1u << (c & 31));
 }
 
@@ -66,11 +69,12 @@ __global__ void __launch_bounds__(1024) scan_rows_kernel(const int32_t* counts, 
 }
 
 __global__ void rank_tiles_kernel(const int32_t* __restrict__ brow, const int32_t* __restrict__ bcol, int64_t nnz,
-                                  int wpr, const uint32_t* __restrict__ bitmap, const int32_t* __restrict__ row_ptr,
-                                  int32_t* __restrict__ block_indices) {
+                                  int nbr, int nbc, int wpr, const uint32_t* __restrict__ bitmap,
+                                  const int32_t* __restrict__ row_ptr, int32_t* __restrict__ block_indices) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nnz) return;
   const int r = brow[i], c = bcol[i];
+  if ((unsigned)r >= (unsigned)nbr || (unsigned)c >= (unsigned)nbc) return;
   const uint32_t* row = bitmap + (size_t)r * wpr;
   int rank = 0;
   for (int w = 0; w < (c >> 5); ++w) rank += __popc(row[w]);
@@ -117,6 +121,65 @@ __global__ void pack_tiles_fp_kernel(const uint4* __restrict__ values, const int
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(v.w) : "f"(__uint_as_float(v.w)));
   }
   packed[g] = v;
+}
+
+// FP8 tiles with their scales folded in, for the row-accumulate kernel: the tensor cores cannot scale a
+// product per tile, so each element a * s_tile / R_row (R_row = the largest tile scale of the tile row) is
+// written as a sum of `terms` E4M3 numbers - the nearest E4M3 value, then the nearest E4M3 value of what is
+// left, and once more for three terms - and every term is multiplied by the same panel of B.  Two terms carry
+// 8 significant bits (relative error below 2^-8 per element, unbiased), three carry 12; the differences
+// x - hi and (x - hi) - mid are exact in fp32.  The epilogue multiplies the row's sums by R_row.
+// One thread per 16-byte chunk of a packed tile, same chunk order as pack_tiles_kernel; term k of packed
+// tile j lies at chunk (j * terms + k) * 64.
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3)));
+}
+template <int TERMS>
+__global__ void pack_tiles_f8_split_kernel(const uint4* __restrict__ values, const float* __restrict__ scales,
+                                           int64_t n_scales, const int32_t* __restrict__ block_rows,
+                                           const int32_t* __restrict__ block_indices,
+                                           const float* __restrict__ row_scale, int64_t nnz,
+                                           uint4* __restrict__ packed) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= nnz * 64) return;
+  const int64_t j = g >> 6;
+  const int q = (int)(g & 63);
+  const int r = (q >> 4) * 8 + (q & 7);
+  const int c16 = (q >> 3) & 1;
+  const int64_t src = block_indices[j];
+  const uint4 v = values[src * 64 + r * 2 + c16];
+  const float s = (scales == nullptr) ? 1.0f : (n_scales == 1 ? scales[0] : scales[src]);
+  const float R = row_scale[block_rows[src]];
+  const float ratio = (R > 0.0f) ? __fdiv_rn(s, R) : 0.0f;
+  const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[TERMS][4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+#pragma unroll
+    for (int k = 0; k < TERMS; ++k) out[k][w] = 0u;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float x = __fmul_rn(e4m3_to_float((uint8_t)(in[w] >> (8 * e))), ratio);
+#pragma unroll
+      for (int k = 0; k < TERMS; ++k) {
+        const uint8_t t = (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+        out[k][w] |= (uint32_t)t << (8 * e);
+        x = __fsub_rn(x, e4m3_to_float(t));
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < TERMS; ++k) packed[(j * TERMS + k) * 64 + q] = make_uint4(out[k][0], out[k][1], out[k][2], out[k][3]);
+}
+
+// largest tile scale of every tile row (0 for an empty row)
+__global__ void row_max_scale_kernel(const int32_t* __restrict__ row_ptr, const float* __restrict__ tile_scales, int nbr,
+                                     float* __restrict__ row_scale) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= nbr) return;
+  float m = 0.0f;
+  for (int t = row_ptr[r]; t < row_ptr[r + 1]; ++t) m = fmaxf(m, tile_scales[t]);
+  row_scale[r] = m;
 }
 
 __global__ void gather_tile_meta_kernel(const int32_t* __restrict__ bcol, const float* __restrict__ scales,
@@ -367,12 +430,15 @@ int void_build_tile_index(const int32_t* block_rows, const int32_t* block_cols, 
   int32_t* counts = reinterpret_cast<int32_t*>(bitmap + (size_t)nbr * wpr);
   if (cudaMemsetAsync(bitmap, 0, (size_t)nbr * wpr * 4, st) != cudaSuccess) return VOID_ERR_CUDA;
   const int tb = 256;
-  if (nnz > 0) mark_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, wpr, bitmap);
+  // every entry of block_indices is a valid position even when the list is rejected afterwards
+  if (nnz > 0 && cudaMemsetAsync(block_indices, 0, (size_t)nnz * 4, st) != cudaSuccess) return VOID_ERR_CUDA;
+  if (nnz > 0)
+    mark_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, nbr, nbc, wpr, bitmap);
   count_rows_kernel<<<(unsigned)(((int64_t)nbr * 32 + tb - 1) / tb), tb, 0, st>>>(bitmap, nbr, wpr, counts);
   scan_rows_kernel<<<1, 1024, 0, st>>>(counts, row_ptr, nbr);
   if (nnz > 0)
-    rank_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, wpr, bitmap, row_ptr,
-                                                                     block_indices);
+    rank_tiles_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_rows, block_cols, nnz, nbr, nbc, wpr, bitmap,
+                                                                     row_ptr, block_indices);
   return last_status();
 }
 
@@ -397,6 +463,39 @@ int void_pack_tiles(const void* values, const float* scales, int64_t n_scales, c
   if (row_scale != nullptr && nbr > 0) {
     if (row_ptr == nullptr || (nnz > 0 && tile_scales == nullptr)) return VOID_ERR_BAD_ARG;
     row_scale_kernel<<<(nbr + tb - 1) / tb, tb, 0, st>>>(row_ptr, tile_scales, nbr, row_scale);
+  }
+  return last_status();
+}
+
+int void_pack_tiles_f8_split(const void* values, const float* scales, int64_t n_scales, const int32_t* block_rows,
+                             const int32_t* block_cols, const int32_t* block_indices, const int32_t* row_ptr, int64_t nnz,
+                             int32_t nbr, int32_t terms, void* packed, int32_t* tile_cols, float* tile_scales,
+                             float* row_scale, void_stream_t stream) {
+  if (nnz < 0 || nbr < 0 || (terms != 2 && terms != 3)) return VOID_ERR_BAD_ARG;
+  if (row_ptr == nullptr || row_scale == nullptr) return VOID_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  const int tb = 256;
+  if (nnz > 0) {
+    if (values == nullptr || block_rows == nullptr || block_cols == nullptr || block_indices == nullptr ||
+        packed == nullptr || tile_cols == nullptr || tile_scales == nullptr)
+      return VOID_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(values) & 15u) != 0 || (reinterpret_cast<uintptr_t>(packed) & 1023u) != 0)
+      return VOID_ERR_ALIGN;
+    if (scales != nullptr && n_scales != 1 && n_scales != nnz) return VOID_ERR_BAD_ARG;
+    gather_tile_meta_kernel<<<(unsigned)((nnz + tb - 1) / tb), tb, 0, st>>>(block_cols, scales, n_scales, block_indices,
+                                                                           nnz, tile_cols, tile_scales);
+  }
+  if (nbr > 0) row_max_scale_kernel<<<(nbr + tb - 1) / tb, tb, 0, st>>>(row_ptr, tile_scales, nbr, row_scale);
+  if (nnz > 0) {
+    const unsigned blocks = (unsigned)((nnz * 64 + tb - 1) / tb);
+    if (terms == 2)
+      pack_tiles_f8_split_kernel<2><<<blocks, tb, 0, st>>>(reinterpret_cast<const uint4*>(values), scales, n_scales,
+                                                           block_rows, block_indices, row_scale, nnz,
+                                                           reinterpret_cast<uint4*>(packed));
+    else
+      pack_tiles_f8_split_kernel<3><<<blocks, tb, 0, st>>>(reinterpret_cast<const uint4*>(values), scales, n_scales,
+                                                           block_rows, block_indices, row_scale, nnz,
+                                                           reinterpret_cast<uint4*>(packed));
   }
   return last_status();
 }

@@ -111,13 +111,20 @@ struct SpmmParams {
   int32_t* partials;
   int32_t* counters;
   int32_t* worker_partials;
+  // Split rows whose sums live on other GPUs (reduction across ranks): n_peers > 0 makes field slot0 of a
+  // segment the owner of its tile row; the row's accumulator, arrival counter and rows of C are the owner's,
+  // reached through peer pointers (peer_out is offset so that the GLOBAL tile row indexes it).
+  int n_peers;
+  int32_t* peer_partials[8];
+  int32_t* peer_counters[8];
+  void* peer_out[8];
   int32_t* status;
   unsigned long long* trace;  // diagnostic instantiations only: 64 timestamps per CTA
   int np;       // panels per work item
+  int terms;    // packed tiles per stored tile: 1, or 2 / 3 when an FP8 tile is stored as a sum of E4M3 terms
   int group;    // tiles per ring stage
   int stages;   // ring depth
   int use3d;    // B panels of a tile fetched by one 3-D TMA
-  int prefetch; // L2 prefetch of the CTA's first work item
   int tma_store;  // 16-bit outputs leave through a staging tile in shared memory and a tiled TMA store
   int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
   int n_items;  // without a plan: nbr * n_chunks
@@ -311,9 +318,9 @@ __device__ __forceinline__ void finish16(const OutDesc& o, int row, int n, int m
   }
 }
 
-// Sixteen finished 16-bit values of output column n into the staging tile [32 m][128 n] in shared memory
+// Sixteen finished 16-bit values of output column n into a staging tile [32 m][PITCH n] in shared memory
 // (stage_col points at element [0][n - n0]); same arithmetic as finish16.
-template <int KIND>
+template <int KIND, int PITCH>
 __device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n, int m0, const uint32_t* r,
                                                float row_scale, float cs, float bias, uint16_t* stage_col) {
   float v[16];
@@ -342,7 +349,7 @@ __device__ __forceinline__ void finish16_stage(const OutDesc& o, int row, int n,
     uint16_t h;
     if (o.dtype == VOID_OUT_F16) h = __half_as_ushort(__float2half_rn(v[k]));
     else h = __bfloat16_as_ushort(__float2bfloat16_rn(v[k]));
-    stage_col[(m0 + k) * kPanelN] = h;
+    stage_col[(m0 + k) * PITCH] = h;
   }
 }
 
@@ -424,7 +431,7 @@ __device__ __forceinline__ uint32_t panel_off(const SpmmParams& p, int j, int q)
 }
 template <int ES>
 __device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
-  return (uint32_t)(p.group * p.np) * (kPanelBytes * ES) + (uint32_t)j * (kTileBytes * ES);
+  return (uint32_t)(p.group * p.np) * (kPanelBytes * ES) + (uint32_t)(j * p.terms) * (kTileBytes * ES);
 }
 
 // Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
@@ -442,6 +449,7 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
                                               int lane, int pw) {
   bool waited = p.a_stable == 0;
   if (waited) grid_dependency_wait();
+  if (TRACE && pw == 0 && lane == 0) stamp<TRACE>(p, 56);   // producer starts
   int begin, end, step;
   seg_range(p, begin, end, step);
   const int G = p.group;
@@ -453,13 +461,21 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     if (i + step < end) seg_next = load_seg(p, i + step);
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
-    const uint32_t unit_bytes = (uint32_t)((kTileBytes + ((p.use3d && !TR) ? p.np : npan) * kPanelBytes) * ES);
+    const uint32_t unit_bytes = (uint32_t)((kTileBytes * p.terms + ((p.use3d && !TR) ? p.np : npan) * kPanelBytes) * ES);
     const int ngroups = (s.t1 - s.t0 + G - 1) / G;
+    if (TRACE && i == begin && pw == 0 && lane == 0) {
+      asm volatile("" ::"r"(s.t1) : "memory");
+      stamp<TRACE>(p, 57);   // the row's tile range has arrived
+    }
     int k = pw - g % C::PW;
     if (k < 0) k += C::PW;
     // block column of this lane's tile in the warp's next group, fetched one group ahead
     int col = 0;
     if (k < ngroups && lane < G && s.t0 + k * G + lane < s.t1) col = __ldg(p.tile_cols + s.t0 + k * G + lane);
+    if (TRACE && i == begin && pw == 0 && lane == 0) {
+      asm volatile("" ::"r"(col) : "memory");
+      stamp<TRACE>(p, 58);   // the first block columns have arrived
+    }
     for (; k < ngroups; k += C::PW) {
       const int gi = g + k;
       const int stage = gi % p.stages;
@@ -478,16 +494,18 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
         ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, ctl) ? 1 : 0;
         if (ok && !drop) {
           mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
-          bulk_load(sbase + tile_off<ES>(p, 0), p.tiles + (size_t)t * (kTileBytes * ES),
-                    (uint32_t)gcnt * (kTileBytes * ES), full);
+          bulk_load(sbase + tile_off<ES>(p, 0), p.tiles + (size_t)t * (size_t)(kTileBytes * ES * p.terms),
+                    (uint32_t)(gcnt * p.terms) * (kTileBytes * ES), full);
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
+      if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 59);   // tiles of the first group requested
       if (!waited) {  // B may be the output of the previous kernel
         grid_dependency_wait();
         waited = true;
       }
+      if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 60);   // past the wait on the previous kernel
       if (lane < gcnt && !drop) {
         if (TR) {
           // B stored transposed ([N, K], k contiguous): one box of 128 rows of n x 32 k per panel
@@ -508,44 +526,6 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     g += ngroups;
   }
   if (!waited) grid_dependency_wait();
-}
-
-// L2 prefetch of everything the CTA's first work item will stream: its packed tiles and the B panels of
-// their block columns.  Without a work plan the first item follows from the block index alone, so the
-// call sits BEFORE the wait on the previous kernel of the stream and its requests travel while that
-// kernel drains (measured on B200: the wait returns about 1 us after the previous kernel's last CTA
-// has ended, and most CTAs of this kernel are resident well before that).  Run by an epilogue warp,
-// which has nothing else to do until the first accumulator is complete.
-// The index arrays read here may not be final yet (the previous kernel could be the one that writes
-// them): they are read around L1 so that no stale line stays behind, every index is clamped into its
-// array, and the values are used for hints only - a wrong hint costs a little bandwidth, never
-// correctness.  With a plan the first item would have to come from the plan's arrays; measured, a
-// prefetch issued after the wait only competes with the ring's own loads, so there is none.
-template <int ES>
-__device__ __forceinline__ void prefetch_first_item(const SpmmParams& p, const CUtensorMap* tmap, int lane) {
-  if (p.tiles == nullptr || p.nnz <= 0 || p.segs != nullptr) return;
-  const int item = (int)blockIdx.x;
-  if (item >= p.n_items) return;
-  const int row = item / p.n_chunks;
-  const int chunk = item - row * p.n_chunks;
-  long long t0 = __ldcv(p.row_ptr + row);
-  long long t1 = __ldcv(p.row_ptr + row + 1);
-  t0 = t0 < 0 ? 0 : (t0 > p.nnz ? p.nnz : t0);
-  t1 = t1 < t0 ? t0 : (t1 > p.nnz ? p.nnz : t1);
-  if (t1 - t0 > 64) t1 = t0 + 64;   // two rounds of the warp are plenty: later tiles ride on the ring's own run-ahead
-  if (t1 == t0) return;
-  if (lane == 0) bulk_prefetch(p.tiles + (size_t)t0 * (kTileBytes * ES), (uint32_t)(t1 - t0) * (kTileBytes * ES));
-  const int npan = panels_in_chunk(p, chunk);
-  const int n0 = chunk * p.np * kPanelN;
-  for (long long t = t0 + lane; t < t1; t += 32) {
-    int col = __ldcv(p.tile_cols + t);
-    col = col < 0 ? 0 : (col >= p.nbc ? p.nbc - 1 : col);
-    if (p.use3d) {
-      tma_prefetch_3d(tmap, 0, col * kTile, chunk * p.np * ES);
-    } else {
-      for (int q = 0; q < npan * ES; ++q) tma_prefetch_2d(tmap, n0 + q * (kPanelN / ES), col * kTile);
-    }
-  }
 }
 
 template <int KIND>
@@ -632,7 +612,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr int ES = Elem<KIND>::ES;
-  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes) * ES);
+  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes * p.terms) * ES);
   const uint32_t acc_cols = (uint32_t)p.np * 32u;  // TMEM columns of one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
@@ -654,7 +634,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       // latency.
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
-      const int G = p.group, S = p.stages, np = p.np;
+      const int G = p.group, S = p.stages, np = p.np, terms = p.terms;
       const uint32_t tiles_at = (uint32_t)(G * np) * (kPanelBytes * ES);
       constexpr uint64_t kPanelStep = (kPanelBytes * ES) >> 4, kTileStep = (kTileBytes * ES) >> 4;
       // one MMA covers 32 bytes of k: 32 / ES k-rows of the panel (8-row groups 1024 bytes apart) and two
@@ -698,11 +678,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll
               for (int kk = 1; kk < ES; ++kk)
                 issue_mma<KIND>(d, adq + kk * kPanelKStep, bd + kk * kTileKStep, idesc, 1u);
+              // a tile stored as a sum of terms: every further term multiplies the same panel
+              if (KIND == VOID_KIND_F8E4M3)
+                for (int u = 1; u < terms; ++u) issue_mma<KIND>(d, adq, bd + (uint64_t)u * kTileStep, idesc, 1u);
               adq += kPanelStep;
               d += 32u;
             }
             ad += kPanelStep * (uint64_t)np;
-            bd += kTileStep;
+            bd += kTileStep * (uint64_t)terms;
             acc = 1u;
           }
           tc_commit(smem_u32(&bars.empty[stage]));
@@ -730,9 +713,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     const uint32_t stage_u32 = ring_base + (uint32_t)p.stages * stage_bytes;
     uint16_t* stage_tile = reinterpret_cast<uint16_t*>(smem_raw + (stage_u32 - smem_u32(smem_raw)));
     bool store_pending = false;
-    // hints for the first work item travel while the previous kernel of the stream drains; then this
-    // role waits for it: the column scales and biases it reads and the C it writes may be that kernel's
-    if (warp == C::EPI0 && p.prefetch) prefetch_first_item<ES>(p, &tmap_b, lane);
+    // the column scales and biases this role reads and the C it writes may be the previous kernel's
     grid_dependency_wait();
     if (epi_tid == 0) stamp<TRACE>(p, 0);
     int begin, end, step;
@@ -746,16 +727,24 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       const int npan = panels_in_chunk(p, s.chunk);
       const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
       const bool has = s.t1 > s.t0;
-      const float rs = (p.row_scale != nullptr) ? __ldg(p.row_scale + s.row) : 1.0f;
+      // an empty tile row is zeros (+ bias): nothing to scale, no scales to wait for
+      const float rs = (p.row_scale != nullptr && (has || s.nseg > 1)) ? __ldg(p.row_scale + s.row) : 1.0f;
       const int n_base = s.chunk * p.np * kPanelN + quad * 32 + lane;
       // per-column scale and bias of the first panel are fetched before the accumulator is ready
       float cs = p.b_scale, bias = 0.0f;
       if (n_base < p.N) {
-        if (p.col_scale != nullptr) cs = __ldg(p.col_scale + n_base) * p.b_scale;
+        if (p.col_scale != nullptr && (has || s.nseg > 1)) cs = __ldg(p.col_scale + n_base) * p.b_scale;
         if (p.bias != nullptr) bias = __ldg(p.bias + n_base);
       }
       // a split row whose scratch index lies outside what the caller provided is skipped and reported
-      const bool bad_split = s.nseg > 1 && (s.ctr < 0 || s.ctr >= p.ctr_limit);
+      const bool peers = p.n_peers > 0 && s.nseg > 1;
+      const bool bad_split = s.nseg > 1 && (s.ctr < 0 || s.ctr >= p.ctr_limit || (peers && (unsigned)s.slot0 >= (unsigned)p.n_peers));
+      int32_t* split_partials = p.partials;
+      int32_t* split_counters = p.counters;
+      if (peers && !bad_split) {
+        split_partials = p.peer_partials[s.slot0];
+        split_counters = p.peer_counters[s.slot0];
+      }
       if (bad_split && epi_tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusBadPlan);
       // one thread waits, the named barrier hands its verdict to all epilogue warps, so that they
       // leave the loop together if the wait gave up
@@ -795,7 +784,27 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
           }
-          if (!TR && p.tma_store) {
+          if (!TR && p.tma_store == 2) {
+            // 16-bit outputs, one store per epilogue warp: the warp puts its 32 x 32 part of the result tile
+            // together in its own 2 KB of shared memory and sends it off itself - no barrier between the warps.
+            // The copy engine clips at the edges of C; the part is free again once the previous store has read it.
+            if (store_pending) {
+              if (lane == 0) bulk_wait_read();
+              __syncwarp();
+            }
+            uint16_t* part = stage_tile + quad * (32 * 32);
+#pragma unroll
+            for (int c = 0; c < C::COLS; c += 16)
+              finish16_stage<KIND, 32>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, part + lane);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stage_u32 + (uint32_t)quad * (32 * 32 * 2), (s.chunk * p.np + q) * kPanelN + quad * 32,
+                           s.row * kTile);
+              bulk_commit();
+            }
+            store_pending = true;
+          } else if (!TR && p.tma_store) {
             // 16-bit outputs: the 32 x 128 result tile is put together in shared memory and leaves in one
             // tiled store; the copy engine clips it at the edges of C.  The staging tile is free again once
             // the previous store has read it.
@@ -805,7 +814,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             }
 #pragma unroll
             for (int c = 0; c < C::COLS; c += 16)
-              finish16_stage<KIND>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, stage_tile + quad * 32 + lane);
+              finish16_stage<KIND, kPanelN>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, stage_tile + quad * 32 + lane);
             fence_proxy_async_smem();
             asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
             if (epi_tid == 0) {
@@ -851,15 +860,23 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
           }
           if (s.nseg == 1) {
             finish8<KIND>(od, s.row, n, m0, r, rs, csq, biasq);
-          } else if (!bad_split) {
+          } else if (!bad_split && has) {
             // partial sum of a split row: added into the row's int32 accumulator in global memory
-            // (integer adds commute, so the total does not depend on which CTA comes first)
-            int32_t* dst = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
+            // (integer adds commute, so the total does not depend on which CTA - or which GPU - comes first)
+            int32_t* dst = split_partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
                            (quad * 32 + lane);
+            if (p.n_peers > 0) {   // the accumulator may be another GPU's: system-wide adds over NVLink
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              if (KIND == VOID_KIND_I8) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
-              else atomicAdd(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
+              for (int k = 0; k < 8; ++k) {
+                if (KIND == VOID_KIND_I8) atomicAdd_system(dst + k * kPanelN, (int32_t)r[k]);
+                else atomicAdd_system(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                if (KIND == VOID_KIND_I8) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
+                else atomicAdd(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
+              }
             }
           }
         }
@@ -867,13 +884,13 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       if (s.nseg > 1 && !bad_split) {
         // the CTA that arrives last reads the completed sums back and finishes the row
         if (epi_tid == 0) stamp<TRACE>(p, 12);
-        __threadfence();
+        if (peers) __threadfence_system(); else __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         if (epi_tid == 0) stamp<TRACE>(p, 13);
         if (epi_tid == 0) {
-          const int old = atomicAdd(p.counters + s.ctr, 1);
+          const int old = peers ? atomicAdd_system(split_counters + s.ctr, 1) : atomicAdd(split_counters + s.ctr, 1);
           const int last = (old == s.nseg - 1) ? 1 : 0;
-          if (last) p.counters[s.ctr] = 0;  // left clean for the next launch
+          if (last) split_counters[s.ctr] = 0;  // left clean for the next launch
           last_s = last;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
@@ -882,7 +899,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (epi_tid == 0) stamp<TRACE>(p, 14);
         if (TRACE && epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
         if (last) {
-          __threadfence();
+          if (peers) __threadfence_system(); else __threadfence();
+          OutDesc od2 = od;
+          od2.acc_out = nullptr;
+          if (peers) od2.out = p.peer_out[s.slot0];   // the owner's rows of C
 #pragma unroll 1
           for (int q = 0; q < npan; ++q) {
             const int n = n_base + q * kPanelN;
@@ -893,13 +913,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             }
             // all of this warp's sums of the panel are requested at once (one L2 round trip), then
             // the accumulator is cleared for the next launch
-            int32_t* src = p.partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
+            int32_t* src = split_partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
                            (quad * 32 + lane);
 #pragma unroll
             for (int c = 0; c < C::COLS; c += 16) {
               uint32_t r[16];
 #pragma unroll
-              for (int k = 0; k < 16; ++k) r[k] = (uint32_t)__ldcg(src + (c + k) * kPanelN);
+              for (int k = 0; k < 16; ++k)
+                r[k] = (uint32_t)(peers ? __ldcv(src + (c + k) * kPanelN) : __ldcg(src + (c + k) * kPanelN));
 #pragma unroll
               for (int k = 0; k < 16; ++k) src[(c + k) * kPanelN] = 0;
               if (od.acc_out != nullptr && n < od.N) {
@@ -907,8 +928,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
 #pragma unroll
                 for (int k = 0; k < 16; ++k) a[(size_t)k * od.N] = r[k];
               }
-              OutDesc od2 = od;
-              od2.acc_out = nullptr;
               finish16<KIND>(od2, s.row, n, m_first + c, r, rs, csq, biasq);
             }
           }
@@ -917,7 +936,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     }
     // the staging tile must have been read before shared memory is given back; the writes themselves
     // complete with the kernel
-    if (store_pending && epi_tid == 0) bulk_wait_read();
+    if (store_pending && (p.tma_store == 2 ? lane == 0 : epi_tid == 0)) bulk_wait_read();
     if (epi_tid == 0) stamp<TRACE>(p, 6);
   }
   pipeline_teardown<C, TRACE>(p, ctl_s, tmem_base, tmem_cols);
@@ -1018,7 +1037,6 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
     const int m_first = half * CW;
     const int G = p.group;
-    if (warp == C::EPI0 && p.prefetch) prefetch_first_item<1>(p, &tmap_b, lane);
     grid_dependency_wait();
     int begin, end, step;
     seg_range(p, begin, end, step);
@@ -1195,7 +1213,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   if (a->act < VOID_ACT_NONE || a->act > VOID_ACT_SILU) return VOID_ERR_BAD_ARG;
   if (a->scale_mode != VOID_SCALE_ROW_MEAN && a->scale_mode != VOID_SCALE_PER_TILE) return VOID_ERR_BAD_ARG;
   if (a->scale_mode == VOID_SCALE_PER_TILE && a->nnz > 0 && a->tile_scales == nullptr) return VOID_ERR_BAD_ARG;
-  if (a->segs != nullptr && a->partials_bytes > 0 && (a->partials == nullptr || a->counters == nullptr)) return VOID_ERR_BAD_ARG;
+  if (a->segs != nullptr && a->partials_bytes > 0 && a->n_peers == 0 && (a->partials == nullptr || a->counters == nullptr))
+    return VOID_ERR_BAD_ARG;
   if ((long long)a->nbr * kTile < a->M) return VOID_ERR_SHAPE;
   const bool tr = a->transposed != 0;
   if (a->transposed != 0 && a->transposed != 1) return VOID_ERR_BAD_ARG;
@@ -1247,12 +1266,16 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   int group = a->tiles_per_stage;  // 0 = default
   if (group == 0) group = (np == 1) ? 4 : 2;  // few, large ring stages beat a deep ring of small ones
   if (a->tiles_per_stage == 0 && floating) group = (es == 2 && np == 1) ? 2 : 1;
-  if (group != 1 && group != 2 && group != 4 && group != 8) return VOID_ERR_BAD_ARG;
+  if (a->tiles_per_stage == 0 && a->tile_terms > 1) group = (np == 1) ? 3 : 1;   // wider tiles: keep four CTAs per SM
+  if (group < 1 || group > 8) return VOID_ERR_BAD_ARG;
   if (drain && np == 1 && shape != 1 && a->tiles_per_stage == 0) group = 2;
   int drain_tmem = 32;   // the largest power of two that lets ctas_per_sm CTAs share the SM's 512 columns
   while (drain_tmem * 2 * ctas_per_sm <= 512) drain_tmem *= 2;
   if (drain && group * np * 32 * 2 > drain_tmem) return VOID_ERR_BAD_ARG;  // two slot groups of products in TMEM
-  const int stage_bytes = group * (np * kPanelBytes + kTileBytes) * es;
+  int terms = a->tile_terms == 0 ? 1 : a->tile_terms;
+  if (terms < 1 || terms > 3) return VOID_ERR_BAD_ARG;
+  if (terms > 1 && (kind != VOID_KIND_F8E4M3 || drain || tr)) return VOID_ERR_BAD_ARG;  // FP8 row-accumulate only
+  const int stage_bytes = group * (np * kPanelBytes + kTileBytes * terms) * es;
   int stages = a->stages;
   if (stages == 0) {
     const int budget = (216 * 1024) / ctas_per_sm - 2048;
@@ -1300,19 +1323,31 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.counters = a->counters;
   p.worker_partials = reinterpret_cast<int32_t*>(a->worker_partials);
   p.status = a->status;
+  p.n_peers = a->n_peers;
+  if (a->n_peers < 0 || a->n_peers > 8) return VOID_ERR_BAD_ARG;
+  if (a->n_peers > 0) {
+    // reduction across GPUs: a plan whose segments name the owner of their tile row; INT8 / floating row-accumulate
+    if (a->segs == nullptr || drain || tr || a->acc_out != nullptr || a->worker_partials != nullptr) return VOID_ERR_BAD_ARG;
+    for (int r = 0; r < a->n_peers; ++r) {
+      if (a->peer_partials[r] == nullptr || a->peer_counters[r] == nullptr || a->peer_out[r] == nullptr) return VOID_ERR_BAD_ARG;
+      p.peer_partials[r] = reinterpret_cast<int32_t*>(a->peer_partials[r]);
+      p.peer_counters[r] = a->peer_counters[r];
+      p.peer_out[r] = a->peer_out[r];
+    }
+  }
   p.trace = reinterpret_cast<unsigned long long*>(a->trace);
   p.np = np;
+  p.terms = terms;
   p.group = group;
   p.stages = stages;
   p.use3d = (!tr && a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
-  p.prefetch = ((a->flags & 1) || tr) ? 0 : 1;
-  p.tma_store = tma_store ? 1 : 0;
+  p.tma_store = tma_store ? ((a->flags & 16) ? 1 : 2) : 0;   // 2: one store per epilogue warp; 1: one per tile
   p.n_items = a->nbr * n_chunks;
   p.a_stable = (a->flags & 4) ? 1 : 0;
   // room of the split-row scratch, in rows: the kernel refuses segments whose counter index lies beyond it
   p.ctr_limit = 0;
-  if (a->segs != nullptr && a->partials != nullptr && a->counters != nullptr && a->partials_bytes > 0) {
+  if (a->segs != nullptr && ((a->partials != nullptr && a->counters != nullptr) || a->n_peers > 0) && a->partials_bytes > 0) {
     const long long rows = a->partials_bytes / ((long long)np * kPanelN * kTile * (long long)sizeof(int32_t));
     p.ctr_limit = rows > 0x7fffffffll ? 0x7fffffff : (int)rows;
   }
@@ -1414,7 +1449,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     if (enc == nullptr) return VOID_ERR_CUDA;
     const cuuint64_t gdim[2] = {(cuuint64_t)a->N, (cuuint64_t)a->M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a->ldc * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kPanelN, (cuuint32_t)kTile};
+    const cuuint32_t box[2] = {(cuuint32_t)((a->flags & 16) ? kPanelN : 32), (cuuint32_t)kTile};
     const cuuint32_t estride[2] = {1, 1};
     if (enc(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a->out, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)

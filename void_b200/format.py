@@ -68,7 +68,18 @@ def build_tile_index(block_rows: torch.Tensor, block_cols: torch.Tensor, nbr: in
         _lib.check(lib.void_build_tile_index(_lib.ptr(br), _lib.ptr(bc), nnz, nbr, nbc, _lib.ptr(row_ptr),
                                              _lib.ptr(block_indices), _lib.ptr(ws), ws_bytes, _lib.stream_ptr(dev)),
                    "void_build_tile_index")
+        check_tile_index(row_ptr, nnz)
     return row_ptr, block_indices
+
+
+def check_tile_index(row_ptr: torch.Tensor, nnz: int) -> None:
+    """The index builder skips block coordinates outside the grid and counts a repeated (row, column) pair
+    once; either shows as fewer indexed tiles than listed ones.  (One read of one integer per built index;
+    the index is cached on its tensor.)"""
+    indexed = int(row_ptr[-1].item())
+    if indexed != nnz:
+        raise ValueError("invalid VOID tile list: %d of %d tiles have block coordinates outside the block grid or "
+                         "repeat an earlier (block_row, block_col) pair" % (nnz - indexed, nnz))
 
 
 @dataclass

@@ -150,6 +150,12 @@ def quantize_to_fp8(tensor: torch.Tensor, config: Optional[FP8Config] = None,
             _lib.check(lib.void_quant_fp8_tiles(_lib.ptr(vf), n, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(scale_inv),
                                                 _lib.ptr(amax), _lib.stream_ptr(dev)), "void_quant_fp8_tiles")
         return q.view(torch.float8_e4m3fn), _fresh_info(config, scale, scale_inv, amax)
+    if config.scale_mode == "per_block" and tensor.dim() >= 2:
+        # one scale per slice of the first dimension (void/fp8.py:97-99): the per-row case of the flattened slices
+        flat = tensor.reshape(tensor.shape[0], -1)
+        q_t, scale, scale_inv = quantize_cols_fp8(flat.t())
+        amax = compute_amax(tensor, "per_block")
+        return q_t.t().contiguous().reshape(tensor.shape), _fresh_info(config, scale, scale_inv, amax)
     if config.scale_mode == "per_row" and tensor.dim() == 2:
         q_t, scale, scale_inv = quantize_cols_fp8(tensor.t())
         amax = compute_amax(tensor, "per_row")
@@ -235,19 +241,47 @@ class FP8VOIDTensor:
         return _spmm.cached_pack(self, self.values_fp8.view(torch.uint8), self.scaling_info.scale, self.block_rows,
                                  self.block_cols, self.shape, _lib.KIND_F8E4M3)
 
+    def packed_split(self, terms: int) -> _spmm.PackedTiles:
+        """Packed copy with the tile scales folded in: every tile as a sum of ``terms`` E4M3 tiles relative to
+        the largest scale of its tile row (built once per ``terms``, cached)."""
+        v, sc = self.values_fp8.view(torch.uint8), self.scaling_info.scale
+        key = (terms, v.data_ptr(), v._version, sc.data_ptr(), sc._version, self.block_rows.data_ptr(),
+               self.block_cols.data_ptr(), str(v.device), tuple(self.shape))
+        cache = self.__dict__.setdefault("_packed_split_cache", {})
+        p = cache.get(terms)
+        if p is None or p.key != key:
+            p = _spmm._mark_ready(_spmm.pack_f8_split(v, sc, self.block_rows, self.block_cols, self.shape, terms))
+            p.key = key
+            cache[terms] = p
+        return p
+
     def __repr__(self) -> str:
         return (f"FP8VOIDTensor(shape={self.shape}, tile_size={self.tile_size}, n_blocks={self.n_blocks}, "
                 f"format={self.scaling_info.config.format.value}, scale_mode={self.scaling_info.config.scale_mode})")
 
 
+DEFAULT_SCALE_TERMS = {torch.float16: 2, torch.bfloat16: 2, torch.float32: 3}
+
+
 def void_spmm_fp8(a: FP8VOIDTensor, b: torch.Tensor, output_dtype: torch.dtype = torch.float16, *,
                   b_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                  activation: int = 0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  activation: int = 0, bias: Optional[torch.Tensor] = None,
+                  scale_terms: Optional[int] = None) -> torch.Tensor:
     """FP8 sparse-dense product C = A @ B (void/fp8.py:674-742).
 
     a: FP8VOIDTensor [M, K];  b: [K, N], either float8_e4m3fn with ``b_scale`` = per-column scales
     [N], or floating point (then quantised to E4M3 per column here).  Returns [M, N] in
     ``output_dtype`` (default float16, as in the reference).
+
+    ``scale_terms`` says how the per-tile scales of A (void/fp8.py:638-646) enter the sum:
+      0     every tile's fp32 product is multiplied by its scale in registers before it is added (the per-tile
+            kernel; exact in fp32, and the slow way: every product is read back from tensor memory);
+      2, 3  the scales are folded into A when it is packed - a * scale / (largest scale of the tile row) stored
+            as a sum of 2 or 3 E4M3 numbers - and the tensor cores accumulate whole tile rows (the row-accumulate
+            kernel).  8 / 12 significant bits of that operand; measured against the exact form the results
+            differ by 4e-4 / 2e-5 of max|C| (the bar of this path is 1e-2, one fp16 rounding is 3e-4).
+      None  2 for 16-bit outputs, 3 for fp32 outputs.
+    With one scale for all tiles (scale_mode="per_tensor") the folded factor is 1 and every form is exact.
     """
     assert b.dim() == 2
     assert a.shape[1] == b.shape[0]
@@ -262,8 +296,15 @@ def void_spmm_fp8(a: FP8VOIDTensor, b: torch.Tensor, output_dtype: torch.dtype =
         b8, col_scale, _ = quantize_cols_fp8(b)
     if out is None:
         out = torch.empty(M, N, dtype=output_dtype, device=b.device)
-    return _spmm.spmm(a.packed(), b8.view(torch.uint8), out, scale_mode=_lib.SCALE_PER_TILE, col_scale=col_scale,
-                      bias=bias, act=activation)
+    if scale_terms is None:
+        scale_terms = DEFAULT_SCALE_TERMS[out.dtype]
+    if scale_terms not in (0, 2, 3):
+        raise ValueError("scale_terms must be 0, 2, 3 or None")
+    if scale_terms == 0:
+        return _spmm.spmm(a.packed(), b8.view(torch.uint8), out, scale_mode=_lib.SCALE_PER_TILE, col_scale=col_scale,
+                          bias=bias, act=activation)
+    return _spmm.spmm(a.packed_split(scale_terms), b8.view(torch.uint8), out, scale_mode=_lib.SCALE_ROW_MEAN,
+                      col_scale=col_scale, bias=bias, act=activation)
 
 
 def void_tensor_to_fp8(void_tensor, format: str = "e4m3", scale_mode: str = "per_block") -> FP8VOIDTensor:
