@@ -400,33 +400,40 @@ def main():
     torch.cuda.synchronize()
     _lib.check_device_status(dev)
 
-    # the K timed steps: replayed CUDA graphs of up to 256 steps each, so that the GPU is not
-    # waiting for the Python launch path between kernels
+    # The timed steps are replayed CUDA graphs, so that the GPU is not waiting for the Python launch path between
+    # kernels.  One pass = exactly K steps.  A replay costs a few microseconds by itself, as much as one step
+    # here, so a small K is captured several passes to a graph (a "block" of ppg passes, about a thousand
+    # launches); a large K is cut into graphs of at most 256 steps.
     K_steps = args.steps
     stream = torch.cuda.Stream(device=dev)
     graphs = []
+    ppg = 1                                   # passes per block
     if not args.no_graph:
-        glen = min(K_steps, 256)
-        while glen > 1 and glen % len(sets) != 0 and glen > len(sets):
-            glen -= 1
+        if K_steps <= 256:
+            ppg = max(1, 1024 // K_steps)
+            glen = K_steps * ppg
+        else:
+            glen = 256
+            while glen > 1 and glen % len(sets) != 0 and glen > len(sets):
+                glen -= 1
         with torch.cuda.stream(stream):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
                 for i in range(glen):
                     step(i)
-            rem = K_steps % glen
+            rem = 0 if ppg > 1 or K_steps <= 256 else K_steps % glen
             g_rem = None
             if rem:
                 g_rem = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g_rem, stream=stream):
                     for i in range(rem):
                         step(i)
-        graphs = [(g, K_steps // glen), (g_rem, 1 if rem else 0)]
+        graphs = [(g, 1 if K_steps <= 256 else K_steps // glen), (g_rem, 1 if rem else 0)]
         with torch.cuda.stream(stream):
             g.replay()
         torch.cuda.synchronize()
 
-    def run_timed():
+    def run_timed():                          # one block: ppg passes of K steps
         with torch.cuda.stream(stream):
             if graphs:
                 for gr, reps in graphs:
@@ -436,9 +443,9 @@ def main():
                 for i in range(K_steps):
                     step(i)
 
-    # One pass = exactly K steps.  A pass of the default K lasts a fraction of a millisecond, too short for
-    # the clock sampler and for a stable mean, so the pass is repeated back to back until the timed region
-    # covers at least MIN_TIMED_MS; every pass is bracketed by its own pair of events on the launching stream.
+    # A block lasts a few milliseconds at most, too short for the clock sampler and for a stable mean, so blocks
+    # are repeated back to back until the timed region covers at least MIN_TIMED_MS; every block is bracketed
+    # by its own pair of events on the launching stream.
     MIN_TIMED_MS = 50.0
     torch.cuda.synchronize()
     if world > 1:
@@ -470,9 +477,10 @@ def main():
     sampler.window[1] = time.perf_counter()
     if world > 1:
         dist.barrier()
-    pass_ms = [marks[r].elapsed_time(marks[r + 1]) for r in range(passes)]
-    ms_total = marks[0].elapsed_time(marks[passes]) / passes      # mean time of one pass of K steps
-    ms_min = min(pass_ms)
+    block_ms = [marks[r].elapsed_time(marks[r + 1]) for r in range(passes)]
+    ms_total = marks[0].elapsed_time(marks[passes]) / (passes * ppg)      # mean time of one pass of K steps
+    ms_min = min(block_ms) / ppg
+    passes *= ppg
     _lib.check_device_status(dev)
 
     # ---- end to end through the public operator with host buffers: every step copies its B (and

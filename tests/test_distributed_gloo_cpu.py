@@ -78,6 +78,27 @@ def _worker(rank, world, port, ret):
         shard2, b2 = void.broadcast_spmm_overlapped(d, b2, s2, src=0, panel_cols=16)
         assert np.array_equal(b2.numpy(), bq) and np.array_equal(s2.numpy(), bs)
         assert shard2.shape == shard.shape and np.array_equal(shard2.numpy(), shard.numpy())
+        # tile-balanced row ranges: shards of unequal height are gathered into the same full result
+        db = void.shard_void_tensor(a, balance="nnz")
+        assert db.row_ranges[0][0] == 0 and db.row_ranges[-1][1] == 9 and db.row_ranges[0][1] == db.row_ranges[1][0]
+        full_b = void.distributed_void_spmm(db, b_t, b_scale=s_t)
+        assert np.array_equal(full_b.numpy(), ref)
+        # COLUMN_WISE / BLOCK_WISE of a floating tensor: local partial products of the whole C, summed by all_reduce
+        # (the reference's route, void/distributed.py:252-267); the shards together give the unsharded product
+        vals32 = (q.astype(np.float32) * s[:, None, None]).astype(np.float32)
+        af = void.VOIDTensor(torch.from_numpy(vals32), torch.from_numpy(rows), torch.from_numpy(cols),
+                             torch.zeros(len(rows), dtype=torch.int64), shape, (32, 32), 0, len(rows), 0.5)
+        bf = torch.from_numpy(bq.astype(np.float32))
+
+        def oracle_fp(local, b, b_scale, out_dtype, out=None):
+            return torch.from_numpy(vo.spmm_fp(local.values.numpy(), local.block_rows.numpy(), local.block_cols.numpy(),
+                                               local.shape, b.numpy())[:local.shape[0]])
+        vd._local_spmm = oracle_fp
+        want = vo.spmm_fp(vals32, rows, cols, shape, bf.numpy())[:shape[0]]
+        for strat in (void.ShardingStrategy.COLUMN_WISE, void.ShardingStrategy.BLOCK_WISE):
+            dc = void.shard_void_tensor(af, strat)
+            got = void.distributed_void_spmm(dc, bf)
+            assert got.shape == want.shape and np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-3), strat
         ret[rank] = "ok"
     except Exception as e:  # pragma: no cover - surfaced through ret
         ret[rank] = repr(e)

@@ -89,3 +89,36 @@ def test_balanced_shard_keeps_order_and_rebases():
         assert d.local_tensor.shape == ((end - start) * 32, vt.shape[1])
         seen.append(ids)
     assert torch.equal(torch.sort(torch.cat(seen)).values, torch.arange(vt.n_blocks))
+
+
+def test_reduce_plan_covers_every_row_once_and_names_its_owner():
+    """Plan of the in-kernel reduction: every (tile row, chunk) appears once per rank, with the owner the
+    ROW_WISE range of the row, a scratch index inside the owner's rows, and this rank's tile range of the row."""
+    from void_b200.reduce import reduce_segments
+    g = np.load(os.path.join(GOLDEN, "shard_small.npz"))
+    vt = _tensor_from_fixture(g)
+    nbr, nbc = vt.block_grid
+    for world in (1, 2, 3, 8):
+        ranges = [vd.row_range(nbr, world, r) for r in range(world)]
+        for strategy in (void.ShardingStrategy.COLUMN_WISE, void.ShardingStrategy.BLOCK_WISE):
+            tiles_seen = 0
+            for rank in range(world):
+                d = void.shard_void_tensor(vt, strategy, world, rank)
+                rows = d.local_tensor.block_rows.long()
+                row_ptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(torch.bincount(rows, minlength=nbr), 0)]).int()
+                for n_chunks, n_cta in ((1, 4), (3, 7), (2, 1000)):
+                    segs, ptr, used = reduce_segments(row_ptr, n_chunks, world, rank, ranges, n_cta)
+                    segs = segs.view(-1, 8).long()
+                    assert segs.shape[0] == nbr * n_chunks and ptr[0] == 0 and ptr[-1] == nbr * n_chunks
+                    assert (torch.diff(ptr.long()) >= 0).all() and ptr.numel() == used + 1
+                    keys = segs[:, 0] * n_chunks + segs[:, 1]
+                    assert torch.equal(torch.sort(keys).values, torch.arange(nbr * n_chunks))
+                    for row, chunk, t0, t1, nseg, owner, me, ctr in segs.tolist():
+                        s, e = ranges[owner]
+                        assert s <= row < e and nseg == world and me == rank
+                        assert ctr == (row - s) * n_chunks + chunk and 0 <= ctr < (e - s) * n_chunks
+                        assert (t0, t1) == (int(row_ptr[row]), int(row_ptr[row + 1]))
+                    if world > 1:       # the first row a rank visits belongs to the next rank
+                        assert segs[0, 5].item() == (rank + 1) % world or ranges[(rank + 1) % world][0] >= nbr
+                tiles_seen += int(row_ptr[-1])
+            assert tiles_seen == vt.n_blocks

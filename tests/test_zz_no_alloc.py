@@ -54,14 +54,45 @@ def test_static_scratch_matches_caller_scratch_twice():
     expected = void.void_spmm_stream_k(q, bq, wl, b_scale=bs, out_dtype=torch.bfloat16, activation=_lib.ACT_GELU,
                                        n_cta=96)
     torch.cuda.synchronize()
+    outs = [torch.full_like(expected, float("nan")) for _ in range(2)]
     for call in range(2):
-        out = torch.full_like(expected, float("nan"))
+        out = outs[call]
         args = _args(q.packed(), plan, bq, bs, out)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         status = lib.void_spmm_i8_static_scratch(ctypes.byref(args), plan.n_counters, _lib.stream_ptr())
         assert status == 0, lib.void_strerror(status)
         torch.cuda.synchronize()
+        if call == 1:     # the first call on a device may load the library's image (array included); later ones take nothing
+            assert torch.cuda.mem_get_info()[0] == free_before
         void.check_device_status()
         assert torch.equal(out, expected), "call %d differs from the caller-scratch result" % call
+
+
+def test_static_scratch_refuses_split_rows_beyond_what_it_cleared():
+    """A plan with more split rows than the caller declared: the rows beyond are skipped and reported through
+    the status word; nothing outside the part of the array the call cleared is touched."""
+    lib = _lib.load()
+    mask = workloads.zipf_mask(128, 512, 1.5, 300, 14.0, seed=13)
+    w = workloads.block_sparse(mask, 256, seed=13)
+    q = void.quantize_void_tensor(w.a)
+    bq, bs = void.quantize_cols_int8(w.b)
+    bq = bq.contiguous()
+    wl = void.compute_stream_k_workload(q)
+    plan = stream_k.stream_k_plan(q, 256, wl, n_cta=96)
+    assert plan.n_counters >= 2
+    out = torch.zeros(q.shape[0], 256, dtype=torch.bfloat16, device="cuda")
+    args = _args(q.packed(), plan, bq, bs, out)
+    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), plan.n_counters - 1, _lib.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(void.VoidB200Error, match="does not fit"):
+        void.check_device_status()
+    # and a correct call afterwards is unaffected
+    expected = void.void_spmm_stream_k(q, bq, wl, b_scale=bs, out_dtype=torch.bfloat16, activation=_lib.ACT_GELU, n_cta=96)
+    assert lib.void_spmm_i8_static_scratch(ctypes.byref(args), plan.n_counters, _lib.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    void.check_device_status()
+    assert torch.equal(out, expected)
 
 
 def test_static_scratch_rejects_oversized_plans():

@@ -156,11 +156,21 @@ def status_word(device):
     return w
 
 
+STATUS_TEXT = {1: "a device-side wait gave up", 2: "a split row of the work plan does not fit the scratch it was given"}
+
+
 def check_device_status(device=None):
-    """Synchronise and raise if a kernel on ``device`` recorded a wait that gave up."""
+    """Synchronise and raise if a kernel on ``device`` recorded a failure in the status word.  The word is
+    cleared, and so is the split-row scratch of every live work plan on the device (a launch that gave up may
+    have left partial sums in it), so that the next launch starts clean."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     w = status_word(dev)
     code = int(w.item())
     if code != 0:
         w.zero_()
-        raise VoidB200Error("void_b200: a device-side wait gave up (status word %d); the output is invalid" % code)
+        from . import _spmm
+        _spmm.reset_plan_scratch(dev)
+        raise VoidB200Error("void_b200: %s (status word %d); the output is invalid"
+                            % (STATUS_TEXT.get(code, "a kernel reported a failure"), code))

@@ -4,6 +4,7 @@ Every function here ends in a call of the C ABI (include/void_b200.h).  Nothing 
 CPU; tensors that are not on a CUDA device are rejected.
 """
 import ctypes
+import weakref
 from dataclasses import dataclass
 from typing import Optional
 
@@ -142,7 +143,22 @@ def cached_pack(owner, values, scales, block_rows, block_cols, shape, kind) -> P
     return p
 
 
-@dataclass
+_LIVE_PLANS = weakref.WeakSet()
+
+
+def reset_plan_scratch(device) -> None:
+    """Zero the split-row accumulators and counters of every live plan on ``device``.  A launch that gave up
+    (status word set) may have left partial sums behind; the kernels only leave the scratch at zero when
+    every split row was finished."""
+    dev = torch.device(device)
+    for plan in list(_LIVE_PLANS):
+        if plan.counters.device == dev:
+            plan.counters.zero_()
+            if plan.partials is not None:
+                plan.partials.zero_()
+
+
+@dataclass(eq=False)
 class Plan:
     """Work plan of void_plan_segments for one (packed tensor, column chunking, CTA count)."""
     segs: torch.Tensor
@@ -225,8 +241,10 @@ def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chun
         if n_ctr:   # one int32 accumulator per split row; the kernel leaves it zero again
             partials = torch.zeros(n_ctr * np_ * PANEL * TILE, dtype=torch.int32, device=dev)
         counters = torch.zeros(max(n_ctr, 1), dtype=torch.int32, device=dev)
-    return Plan(segs, cta_seg_ptr, n_cta, np_, n_chunks, n_segs, n_slots, n_ctr, partials, counters, mode,
+    plan = Plan(segs, cta_seg_ptr, n_cta, np_, n_chunks, n_segs, n_slots, n_ctr, partials, counters, mode,
                 chunk_tiles)
+    _LIVE_PLANS.add(plan)
+    return plan
 
 
 def prepare_b(b: torch.Tensor, elem_bytes: int = 1) -> torch.Tensor:

@@ -235,7 +235,11 @@ def _local_spmm(local, b, b_scale, out_dtype, out=None):
         return void_spmm_int8(local, b, b_scale, out, out_dtype=out_dtype)
     if isinstance(local, FP8VOIDTensor):
         return void_spmm_fp8(local, b, out_dtype or torch.float16, b_scale=b_scale, out=out)
-    raise NotImplementedError("distributed_void_spmm on B200 takes shards of Int8VOIDTensor or FP8VOIDTensor")
+    if isinstance(local, VOIDTensor):
+        from .ops import void_spmm
+        res = void_spmm(local, b, out)
+        return res if out_dtype in (None, res.dtype) else res.to(out_dtype)
+    raise NotImplementedError("distributed_void_spmm takes shards of VOIDTensor, Int8VOIDTensor or FP8VOIDTensor")
 
 
 def broadcast_spmm_overlapped(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, scales: Optional[torch.Tensor] = None,
@@ -316,38 +320,65 @@ class _NullContext:
         return False
 
 
-def distributed_void_spmm(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
-                          async_op: bool = False, *, b_scale=None, out_dtype: Optional[torch.dtype] = None,
-                          gather_output: bool = True) -> torch.Tensor:
-    """C = A @ B with A sharded by tile rows (void/distributed.py:199-270).
-
-    b must be replicated on every rank (see broadcast_b).  With gather_output=True the full [M, N]
-    result is returned on every rank like the reference does (:234-250); with gather_output=False
-    each rank returns its own row shard [(end - start) * tile_m, N] and no collective runs.
-    """
-    if dist_tensor.strategy != ShardingStrategy.ROW_WISE:
-        raise NotImplementedError("void_b200 shards ROW_WISE only")
-    M, K = dist_tensor.global_shape
-    N = b.shape[1]
-    local_out = _local_spmm(dist_tensor.local_tensor, b, b_scale, out_dtype, out if not gather_output else None)
-    if dist_tensor.world_size == 1 or not gather_output:
-        return local_out[:M] if dist_tensor.world_size == 1 else local_out
-    tile_m = dist_tensor.local_tensor.tile_size[0]
-    n_block_rows = (M + tile_m - 1) // tile_m
-    rows_per_rank = (n_block_rows + dist_tensor.world_size - 1) // dist_tensor.world_size
-    # equal-sized buffers for all_gather: pad the last shard to rows_per_rank tile rows
-    padded = torch.zeros(rows_per_rank * tile_m, N, dtype=local_out.dtype, device=local_out.device)
-    padded[:local_out.shape[0]] = local_out
-    gathered = [torch.empty_like(padded) for _ in range(dist_tensor.world_size)]
+def _gather_rows(shard: torch.Tensor, ranges, rank: int, M: int, tile_m: int, out: Optional[torch.Tensor]) -> torch.Tensor:
+    """all_gather of row shards of unequal height (padded to the tallest) into the full [M, N] result."""
+    N = shard.shape[1]
+    rows_max = max(e - s for s, e in ranges) * tile_m
+    padded = torch.zeros(rows_max, N, dtype=shard.dtype, device=shard.device)
+    padded[:shard.shape[0]] = shard
+    gathered = [torch.empty_like(padded) for _ in ranges]
     dist.all_gather(gathered, padded)
     if out is None:
-        out = torch.empty(M, N, dtype=local_out.dtype, device=local_out.device)
-    for r, g in enumerate(gathered):
-        start = r * rows_per_rank * tile_m
-        end = min(start + g.shape[0], M)
+        out = torch.empty(M, N, dtype=shard.dtype, device=shard.device)
+    for (s, e), g in zip(ranges, gathered):
+        start, end = s * tile_m, min(e * tile_m, M)
         if end > start:
             out[start:end] = g[:end - start]
     return out
+
+
+def distributed_void_spmm(dist_tensor: DistributedVOIDTensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+                          async_op: bool = False, *, b_scale=None, out_dtype: Optional[torch.dtype] = None,
+                          gather_output: bool = True) -> torch.Tensor:
+    """C = A @ B with A sharded over the ranks (void/distributed.py:199-270).
+
+    b must be replicated on every rank (see broadcast_b).
+    ROW_WISE: every rank multiplies its tile rows; with gather_output=True the full [M, N] result is returned
+    on every rank like the reference does (:234-250), with gather_output=False each rank returns its own row
+    shard [(end - start) * tile_m, N] and no collective runs.
+    COLUMN_WISE / BLOCK_WISE: the per-rank products are partial sums of all of C (:252-267).  For Int8 shards on
+    GPUs the sum happens inside the kernel (reduce.fused_reduce_spmm: every rank ends up with the finished rows
+    it owns, which gather_output=True then gathers); other tensors take the reference's route, a local product
+    followed by dist.all_reduce of the full result.
+    """
+    import dataclasses
+    M, K = dist_tensor.global_shape
+    local = dist_tensor.local_tensor
+    tile_m = local.tile_size[0]
+    ranges = dist_tensor.owner_ranges()
+    if dist_tensor.strategy != ShardingStrategy.ROW_WISE:
+        whole = dataclasses.replace(local, shape=(M, K)) if tuple(local.shape) != (M, K) else local
+        if dist_tensor.world_size == 1:
+            return _local_spmm(whole, b, b_scale, out_dtype, out)
+        if isinstance(local, Int8VOIDTensor) and b.is_cuda and dist_tensor.global_row_scale is not None:
+            from .reduce import fused_reduce_spmm
+            shard = fused_reduce_spmm(dist_tensor, b, b_scale, out_dtype)
+            if not gather_output:
+                return shard
+            return _gather_rows(shard, ranges, dist_tensor.rank, M, tile_m, out)
+        if isinstance(local, Int8VOIDTensor):
+            raise NotImplementedError("Int8 shards by column or block need the whole rows' mean scales: shard on the GPU")
+        partial = _local_spmm(whole, b, b_scale, torch.float32)
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM)
+        res = partial if out_dtype in (None, torch.float32) else partial.to(out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    local_out = _local_spmm(local, b, b_scale, out_dtype, out if not gather_output else None)
+    if dist_tensor.world_size == 1 or not gather_output:
+        return local_out[:M] if dist_tensor.world_size == 1 else local_out
+    return _gather_rows(local_out, ranges, dist_tensor.rank, M, tile_m, out)
 
 
 __all__ = ["ShardingStrategy", "DistributedVOIDTensor", "shard_void_tensor", "distributed_void_spmm", "broadcast_b",
