@@ -98,6 +98,7 @@ def parse_args():
     ap.add_argument("--sparsity", type=float, default=0.9)
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling record of a multi-GPU run")
     ap.add_argument("--copies", type=int, default=0, help="distinct input copies to rotate over (0 = enough for L2)")
     return ap.parse_args()
 
@@ -260,6 +261,126 @@ def cpu_workload(args, np, torch, vo):
 
 
 # ----------------------------------------------------------------------------------------------
+def strong_scaling_record(torch, dist, void, workloads, _lib, dev, rank, world):
+    """The multi-GPU workload, measured in the same run as the weak-scaling line: A 65536 x 65536 at 95 % block
+    sparsity, INT8 per block, B 65536 x 1024 INT8 per column, fp16 row shards.  Total work is fixed:
+      ms_1gpu        rank 0 alone multiplies all 2048 tile rows (the other ranks idle at a barrier);
+      ms_per_step    every rank multiplies its ROW_WISE shard, no collective in the step, max over ranks;
+      column_wise_*  the same product from COLUMN_WISE shards, summed over ranks inside the kernel (every rank
+                     ends with the finished rows it owns), next to what an NCCL all_reduce of the fp32 [M, N]
+                     partial results alone would cost (the reference's way of adding them).
+    Every rank generates the same A from one seed and shards it; B is made on rank 0 and broadcast.  Steps rotate
+    over two copies of B and C so that a rank's working set (27 MB of A at eight ranks) does not stay in L2."""
+    import time as _time
+    N, K = 1024, 65536
+    full, _, nnz = workloads.sharded_int8(world_size=1, rank=0, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    if rank == 0:
+        b = torch.randn(K, N, generator=g).to(dev)
+        bq0, bs0 = void.quantize_cols_int8(b)
+        bq0 = bq0.contiguous()
+        del b
+    else:
+        bq0 = torch.empty(K, N, dtype=torch.int8, device=dev)
+        bs0 = torch.empty(N, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    void.broadcast_b(bq0, src=0, scales=bs0)              # warm the channels
+    e0.record()
+    void.broadcast_b(bq0, src=0, scales=bs0)
+    e1.record()
+    torch.cuda.synchronize()
+    bcast = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(bcast, op=dist.ReduceOp.MAX)
+    bqs = [bq0, torch.roll(bq0, 1, 0).contiguous()]
+
+    def timed(fn, steps, graph=True):
+        for i in range(4):
+            fn(i)
+        torch.cuda.synchronize()
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            if graph:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=st):
+                    for i in range(steps):
+                        fn(i)
+                run = gr.replay
+            else:
+                run = lambda: [fn(i) for i in range(steps)]
+            run()
+            torch.cuda.synchronize()
+            dist.barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 4
+            t0.record(st)
+            for _ in range(reps):
+                run()
+            t1.record(st)
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / (reps * steps)
+
+    # ---- ROW_WISE shards, every rank at once
+    d = void.shard_void_tensor(full, void.ShardingStrategy.ROW_WISE)
+    shard = d.local_tensor
+    outs = [torch.empty(shard.shape[0], N, dtype=torch.float16, device=dev) for _ in range(2)]
+    ms_n = timed(lambda i: void.void_spmm_int8(shard, bqs[i % 2], bs0, outs[i % 2]), 20)
+    t = torch.tensor([ms_n], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_n = float(t.item())
+    _lib.check_device_status(dev)
+    del outs
+
+    # ---- one GPU alone on the whole matrix
+    ms_1 = 0.0
+    if rank == 0:
+        outs1 = [torch.empty(full.shape[0], N, dtype=torch.float16, device=dev) for _ in range(2)]
+        for i in range(4):
+            void.void_spmm_int8(full, bqs[i % 2], bs0, outs1[i % 2])
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(40):
+            void.void_spmm_int8(full, bqs[i % 2], bs0, outs1[i % 2])
+        t1.record()
+        torch.cuda.synchronize()
+        ms_1 = t0.elapsed_time(t1) / 40
+        del outs1
+    t = torch.tensor([ms_1], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_1 = float(t.item())
+
+    # ---- COLUMN_WISE shards, summed inside the kernel; and the all_reduce the reference would run instead
+    col = {}
+    try:
+        dc = void.shard_void_tensor(full, void.ShardingStrategy.COLUMN_WISE)
+        fn = lambda i: void.distributed_void_spmm(dc, bqs[i % 2], b_scale=bs0, out_dtype=torch.float16, gather_output=False)
+        ms_c = timed(fn, 10, graph=False)
+        part = torch.zeros(full.shape[0], N, dtype=torch.float32, device=dev)
+        ms_ar = timed(lambda i: dist.all_reduce(part), 5, graph=False)
+        t = torch.tensor([ms_c, ms_ar], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        scratch = next(iter(dc.__dict__["_reduce_states"].values())).scratch
+        col = {"column_wise_fused_ms": float(t[0]), "allreduce_fp32_result_only_ms": float(t[1]),
+               "peer_memory": "symmetric memory" if not isinstance(scratch.keep, tuple) else "CUDA IPC"}
+        _lib.check_device_status(dev)
+    except Exception as ex:                                  # the row-shard numbers stand without it
+        col = {"column_wise_error": repr(ex)[:200]}
+
+    rows_local = shard.shape[0] // 32
+    np_ = 2
+    items = rows_local * (N // 128 // np_)
+    ctas = 4 * void._spmm.sm_count(dev)
+    a_mb, b_mb, c_mb = shard.n_blocks * 1032 / 1e6, K * N / 1e6, shard.shape[0] * N * 2 / 1e6
+    limiter = ("every rank reads all of B: %.0f MB of its %.0f MB per launch; %d work items on %d resident CTAs = %.2f waves"
+               % (b_mb, a_mb + b_mb + c_mb, items, ctas, items / ctas))
+    return {"workload": STRONG_WORKLOAD, "nnz_tiles": int(nnz), "ms_1gpu": ms_1, "ms_per_step": ms_n,
+            "speedup": ms_1 / ms_n if ms_n > 0 else None, "efficiency": ms_1 / ms_n / world if ms_n > 0 else None,
+            "tops": workloads.spmm_ops(int(nnz), N) / (ms_n * 1e-3) / 1e12 if ms_n > 0 else None,
+            "b_broadcast_ms": float(bcast.item()), "l2": "two copies of B and C in rotation", "limiter": limiter, **col}
+
+
 def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
     """Per-rank operands: a list of (A quantised, B 8-bit, B scales, out) copies to rotate over."""
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -639,6 +760,8 @@ def main():
         first_step = {"broadcast_then_spmm_ms": float(ts[0]), "overlapped_panels_ms": float(ts[1]), "panel_cols": 256}
 
     strong = None
+    if world > 1 and args.workload == "headline" and not args.no_strong:
+        strong = strong_scaling_record(torch, dist, void, workloads, _lib, dev, rank, world)
     # ---- aggregate over ranks: max time, summed work
     t = torch.tensor([ms_total, e2e_ms, e2e_serial_ms, ms_min], dtype=torch.float64, device=dev)
     work = torch.tensor([ops_per_step_local, float(np.mean(nnz_local))], dtype=torch.float64, device=dev)
