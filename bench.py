@@ -18,6 +18,7 @@ batch of synthetic input.  Workloads:
   powerlaw            16384 x 16384, Zipf(1.5) tile-row lengths, N = 256, INT8, Stream-K + GELU, bf16 out.
   sharded             65536 x 65536 at 95 %, N = 1024, INT8, ROW_WISE shards over the ranks (strong
                       scaling: the total work is fixed).
+  mid                 16384 x 16384 at 90 %, N = 1024, INT8: a tensor-bound case small enough to profile.
 
 value  = whole-job TOPS over the nonzero tiles (2*nnz*32*32*N per step) with inputs resident in HBM.
 e2e    = the same metric through the public operator with HOST buffers: every step copies that step's
@@ -41,7 +42,7 @@ METRIC = "block_sparse_spmm_tops_nonzero_tiles"
 # dram__bytes_write.sum of one launch), it is not measured by this run
 PROFILE_OF = {"headline": "spmm_rowacc_int8_headline.md", "fp8": "spmm_rowacc_fp8_headline.md",
               "powerlaw": "spmm_rowacc_int8_powerlaw_streamk.md", "fp32": "spmm_rowacc_tf32_headline.md",
-              "sharded": "spmm_rowacc_int8_sharded65536.md"}
+              "sharded": "spmm_rowacc_int8_sharded65536.md", "mid": "spmm_rowacc_int8_mid16384.md"}
 L2_BYTES = 126 * 1024 * 1024
 STRONG_WORKLOAD = "uniform65536_bs95_n1024"
 
@@ -74,6 +75,10 @@ def workload_config(args, world):
     if args.workload == "powerlaw":
         nnz = int(workloads.zipf_mask(512, 512, 1.5, 512, 15.36, 0).sum())
         cfg = {"workload": "zipf16384_n256_streamk_gelu", "M_per_gpu": 16384, "K": 16384, "N": 256, "out_dtype": "bfloat16"}
+    elif args.workload == "mid":
+        nnz = int(workloads.uniform_mask(512, 512, args.sparsity, 0).sum())
+        cfg = {"workload": "uniform16384_bs%02d_n1024" % round(args.sparsity * 100), "M_per_gpu": 16384, "K": 16384,
+               "N": 1024, "out_dtype": "float16"}
     elif args.workload == "sharded":
         nnz = int(round(2048 * 2048 * 0.05))
         cfg = {"workload": STRONG_WORKLOAD + "_rowshards", "M_per_gpu": 65536 // world, "K": 65536, "N": 1024,
@@ -94,7 +99,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded", "fp32", "fp16"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded", "fp32", "fp16", "mid", "floor"])
+    ap.add_argument("--min-timed-ms", type=float, default=50.0, help="repeat the K steps until the timed region lasts this long")
     ap.add_argument("--sparsity", type=float, default=0.9)
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -261,6 +267,62 @@ def cpu_workload(args, np, torch, vo):
 
 
 # ----------------------------------------------------------------------------------------------
+def launch_floor(args, torch, void, workloads, _lib, _spmm, dev):
+    """What a launch of the headline's shape costs before any work, in the harness of the timed steps (CUDA graph
+    of 512 launches back to back, rotating input copies): an empty kernel with the same grid, block, shared memory
+    and launch attribute; the SpMM over an EMPTY A of the same shape; and the SpMM itself with its switches."""
+    import numpy as np
+    import scipy.sparse as sp
+    lib = _lib.load()
+    ns = args.copies if args.copies > 0 else 34
+    sets = []
+    for i in range(ns):
+        w = workloads.headline(args.sparsity, seed=i, device=dev)
+        q = void.quantize_void_tensor(w.a)
+        bq, bs = void.quantize_cols_int8(w.b)
+        sets.append((q.packed(), bq.contiguous(), bs, torch.empty(4096, 512, dtype=torch.float16, device=dev)))
+    empty = void.quantize_void_tensor(void.csr_to_void(sp.csr_matrix((4096, 4096), dtype=np.float32), device=dev)).packed()
+    torch.cuda.synchronize()
+
+    def timed(fn, steps=512, reps=8):
+        for i in range(8):
+            fn(i)
+        torch.cuda.synchronize()
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for i in range(steps):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(reps):
+                g.replay()
+            e1.record(st)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (reps * steps) * 1e3
+
+    def spmm(pk, **kw):
+        def fn(i):
+            _, bq, bs, out = sets[i % ns]
+            _spmm.spmm(pk(i), bq, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=bs, **kw)
+        return fn
+    own = lambda i: sets[i % ns][0]
+    res = {
+        "null_kernel_us": timed(lambda i: lib.void_launch_floor(512, 224, 50176, _lib.stream_ptr(dev))),
+        "empty_a_us": timed(spmm(lambda i: empty)),
+        "spmm_us": timed(spmm(own)),
+        "spmm_one_store_per_tile_us": timed(spmm(own, flags=_spmm.FLAG_STORE_PER_TILE)),
+        "spmm_direct_stores_us": timed(spmm(own, flags=_spmm.FLAG_DIRECT_STORES)),
+        "spmm_a_not_read_early_us": timed(spmm(own, flags=_spmm.FLAG_NO_EARLY_A)),
+    }
+    _lib.check_device_status(dev)
+    print(json.dumps({"workload": "floor", "shape": "uniform4096_bs%02d_n512" % round(args.sparsity * 100),
+                      "input_copies": ns, "launches_per_graph": 512, **{k: round(v, 3) for k, v in res.items()}}))
+
+
 def strong_scaling_record(torch, dist, void, workloads, _lib, dev, rank, world):
     """The multi-GPU workload, measured in the same run as the weak-scaling line: A 65536 x 65536 at 95 % block
     sparsity, INT8 per block, B 65536 x 1024 INT8 per column, fp16 row shards.  Total work is fixed:
@@ -405,6 +467,10 @@ def build_rank_inputs(args, rank, world, torch, void, workloads, copies_hint):
     if args.workload == "powerlaw":
         make = lambda seed: workloads.power_law(seed=seed, device=dev)
         N, out_dtype, kind = 256, torch.bfloat16, "i8"
+    elif args.workload == "mid":
+        make = lambda seed: workloads.block_sparse(workloads.uniform_mask(512, 512, args.sparsity, seed), 1024, seed, dev,
+                                                   "uniform16384_bs%02d_n1024" % round(args.sparsity * 100))
+        N, out_dtype, kind = 1024, torch.float16, "i8"
     else:
         make = lambda seed: workloads.headline(args.sparsity, seed=seed, device=dev)
         N, out_dtype, kind = 512, torch.float16, ("f8e4m3" if args.workload == "fp8" else "i8")
@@ -475,6 +541,10 @@ def main():
     if args.gpus != world and rank == 0:
         print("bench.py: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (args.gpus, world), file=sys.stderr)
 
+    if args.workload == "floor":
+        if rank == 0:
+            launch_floor(args, torch, void, workloads, _lib, _spmm, dev)
+        return
     sampler = ClockSampler(local_rank)
     sampler.start()
 
@@ -567,7 +637,7 @@ def main():
     # A block lasts a few milliseconds at most, too short for the clock sampler and for a stable mean, so blocks
     # are repeated back to back until the timed region covers at least MIN_TIMED_MS; every block is bracketed
     # by its own pair of events on the launching stream.
-    MIN_TIMED_MS = 50.0
+    MIN_TIMED_MS = args.min_timed_ms
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -816,7 +886,7 @@ def main():
             "gpu_launches": passes * K_steps,
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline and world == 1 and args.workload != "sharded":
+        if not args.no_cpu_baseline and world == 1 and args.workload not in ("sharded", "mid"):
             from oracle import void_oracle as vo
             cfg, run, cores = cpu_workload(args, np, torch, vo)
             run()

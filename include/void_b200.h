@@ -404,6 +404,11 @@ VOID_API int void_spmm_tile_grad(const void* grad_out, int64_t ldg, const void* 
  * library, until the process exits.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current); make that first call outside any stream capture.
+ * "Allocates nothing" is about the calls: the array is part of the library's device image, and the CUDA
+ * runtime reserves device memory for that image (these 8 MiB + 16 KiB included) when the library is first
+ * used on a device (with lazy module loading: at the first call that launches a kernel or asks for the
+ * array's address).  An embedder whose own allocator is going to claim the rest of the GPU should make its
+ * first call of this entry point on each device - any small product - before it does so.
  * All calls on a device share the one array, and it keeps the previous call's contents: the part
  * a call uses (accumulators and counters) is cleared in stream order before its launch.  Two
  * calls that overlap on the GPU (different streams, or different host threads on one device)

@@ -1153,9 +1153,11 @@ struct DeviceInfo {
 };
 static DeviceInfo device_info() {
   static DeviceInfo cache[64];
+  static std::mutex mu;
   int dev = 0;
   DeviceInfo none;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return none;
+  std::lock_guard<std::mutex> lock(mu);   // a record is filled and read under the lock: no half-written fields
   if (!cache[dev].ok) {
     DeviceInfo d;
     if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return none;
@@ -1169,10 +1171,13 @@ static DeviceInfo device_info() {
 }
 
 // cudaFuncSetAttribute per (kernel, device), repeated only when a larger ring is asked for.
-// All kernels share one C++ function-pointer type, so the record is keyed by the pointer value.
+// All kernels share one C++ function-pointer type, so the record is keyed by the pointer value.  The table
+// holds every instantiation of this file on up to 16 devices; beyond that the attribute is simply set again
+// on every launch of the pairs that found no room (correct, a little slower).
 static int ensure_smem(const void* kernel, int bytes) {
   struct Rec { const void* fn; int dev; int bytes; };
-  static Rec recs[64];
+  constexpr int kRecs = 48 * 16;
+  static Rec recs[kRecs];
   static int n_recs = 0;
   static std::mutex mu;
   int dev = 0;
@@ -1183,7 +1188,7 @@ static int ensure_smem(const void* kernel, int bytes) {
     if (recs[i].fn == kernel && recs[i].dev == dev) r = &recs[i];
   if (r != nullptr && r->bytes >= bytes) return 0;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
-  if (r == nullptr && n_recs < 64) r = &recs[n_recs++];
+  if (r == nullptr && n_recs < kRecs) r = &recs[n_recs++];
   if (r != nullptr) { r->fn = kernel; r->dev = dev; r->bytes = bytes; }
   return 0;
 }
