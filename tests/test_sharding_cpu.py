@@ -122,3 +122,12 @@ def test_reduce_plan_covers_every_row_once_and_names_its_owner():
                         assert segs[0, 5].item() == (rank + 1) % world or ranges[(rank + 1) % world][0] >= nbr
                 tiles_seen += int(row_ptr[-1])
             assert tiles_seen == vt.n_blocks
+
+
+def test_tile_list_with_repeated_or_out_of_range_coordinates_is_rejected():
+    """The device index builder skips coordinates outside the grid and counts a repeated pair once; the host
+    check that follows it compares the indexed count with the listed one."""
+    from void_b200.format import check_tile_index
+    check_tile_index(torch.tensor([0, 2, 2, 5], dtype=torch.int32), 5)            # consistent: accepted
+    with pytest.raises(ValueError, match="1 of 5 tiles"):
+        check_tile_index(torch.tensor([0, 2, 2, 4], dtype=torch.int32), 5)

@@ -713,14 +713,16 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     const uint32_t stage_u32 = ring_base + (uint32_t)p.stages * stage_bytes;
     uint16_t* stage_tile = reinterpret_cast<uint16_t*>(smem_raw + (stage_u32 - smem_u32(smem_raw)));
     bool store_pending = false;
-    // the column scales and biases this role reads and the C it writes may be the previous kernel's
-    grid_dependency_wait();
-    if (epi_tid == 0) stamp<TRACE>(p, 0);
+    // the column scales and biases this role reads and the C it writes may be the previous kernel's; the index
+    // of A may be read ahead of it when the caller vouches for A
+    if (!p.a_stable) grid_dependency_wait();
     int begin, end, step;
     seg_range(p, begin, end, step);
     uint32_t it = 0;
     Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
     if (begin < end) seg_next = load_seg(p, begin);
+    if (p.a_stable) grid_dependency_wait();
+    if (epi_tid == 0) stamp<TRACE>(p, 0);
     for (int i = begin; i < end; i += step, ++it) {
       const Seg s = seg_next;
       if (i + step < end) seg_next = load_seg(p, i + step);
@@ -747,7 +749,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       }
       if (bad_split && epi_tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, kStatusBadPlan);
       // one thread waits, the named barrier hands its verdict to all epilogue warps, so that they
-      // leave the loop together if the wait gave up
+      // leave the loop together if the wait gave up (a warp that went on alone would wait at the next
+      // named barrier for ever)
       if (epi_tid == 0) ok_s[it & 1u] = mbar_wait(smem_u32(&bars.acc_full[buf]), aph, ctl) ? 1 : 0;
       asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
       if (!ok_s[it & 1u]) break;
