@@ -253,6 +253,7 @@ def main():
     c_block_rawb = ref_fp8_spmm(a8, b8.float().t().contiguous())      # unit B scales (epilogue check)
     c_tensor = ref_fp8_spmm(a8t, b_deq)
     c_f16 = ref_fp8_spmm(a8, b_deq, torch.float16)
+    c_floatb = ref_fp8_spmm(a8, b)                # B given in floating point: used as it is
     kat = torch.tensor([[[1.0, 2.0], [3.0, 4.0]], [[5.0, 6.0], [7.0, 8.0]]])
     save("fp8_small.npz", **coo_inputs(m), b=b.numpy(), block_rows=a8.block_rows.numpy(),
          block_cols=a8.block_cols.numpy(), a_fp8=a8.values_fp8.view(torch.uint8).numpy(),
@@ -261,7 +262,7 @@ def main():
          at_fp8=a8t.values_fp8.view(torch.uint8).numpy(), at_scale=a8t.scaling_info.scale.reshape(1).numpy(),
          b_fp8=b8.t().contiguous().view(torch.uint8).numpy(), b_scale=binfo.scale.numpy(),
          b_scale_inv=binfo.scale_inv.numpy(), c_block=c_block.numpy(), c_block_rawb=c_block_rawb.numpy(),
-         c_tensor=c_tensor.numpy(), c_f16=c_f16.float().numpy(),
+         c_tensor=c_tensor.numpy(), c_f16=c_f16.float().numpy(), c_floatb=c_floatb.numpy(),
          kat_amax_tensor=compute_amax(kat, "per_tensor").reshape(1).numpy(),
          kat_amax_block=compute_amax(kat, "per_block").numpy())
 

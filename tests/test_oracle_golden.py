@@ -199,6 +199,9 @@ def test_fp8_spmm():
     ct = vo.spmm_fp8(g["at_fp8"], g["at_scale"], g["block_rows"], g["block_cols"], shape, b_deq, per_tensor=True)
     assert rel_err(ct, g["c_tensor"]) < 1e-6
     assert rel_err(c.astype(np.float16).astype(np.float32), g["c_f16"]) < 1e-3
+    # a floating-point B is used as it is
+    cf = vo.spmm_fp8(g["a_fp8"], g["a_scale"], g["block_rows"], g["block_cols"], shape, g["b"])
+    assert rel_err(cf, g["c_floatb"]) < 1e-6
 
 
 def test_gelu_matches_reference_kernel():

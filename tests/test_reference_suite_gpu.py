@@ -25,6 +25,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+@pytest.fixture(autouse=True)
+def _seeded():
+    """The reference's tests draw B and the scipy matrices without a seed, and some of their bars are relative
+    errors averaged over elements that can be arbitrarily close to zero; the restated tests fix the seeds so that a
+    run is repeatable."""
+    torch.manual_seed(20250)
+    np.random.seed(20250)
+
+
 def _small():       # tests/conftest.py:29-33 and tests/test_fp8.py:29-37
     np.random.seed(42)
     return sp.random(256, 256, density=0.1, format="csr", dtype=np.float32)

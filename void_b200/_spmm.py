@@ -214,7 +214,7 @@ def streamk_table(row_ptr: torch.Tensor, nbr: int, nnz: int, n_workers: Optional
     return rows[:n], start[:n], end[:n], atomic[:n].to(torch.bool), woff, target
 
 
-ROW_COST = 6   # epilogue of one (tile row, chunk) in units of one tile's work, measured on B200
+ROW_COST = 12  # epilogue of one (tile row, chunk) in units of one tile of work, swept on B200 (power-law workload: 6 -> 22.0 us, 12 -> 19.9, 24 -> 21.4)
 
 
 def make_plan(packed: PackedTiles, N: int, np_: int, n_cta: int, mode: int, chunk_tiles: int = 0,

@@ -840,22 +840,27 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
           if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
           if (p.bias != nullptr) biasq = __ldg(p.bias + n);
         }
-#pragma unroll 1
+        // (raw accumulators wanted, or a piece of a split row) all columns of the panel with one wait, then the
+        // accumulator buffer goes back to the MMA warp
+        uint32_t ra[C::COLS];
+        if (has) {
+          tmem_ld_cols<C::COLS>(acc_addr, ra);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int k = 0; k < C::COLS; ++k) ra[k] = 0u;
+        }
+        if (q == npan - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
+        }
+#pragma unroll
         for (int c = 0; c < C::COLS; c += 8) {
           const int m0 = m_first + c;
           uint32_t r[8];
-          if (has) {
-            tmem_ld_32x8(acc_addr + (uint32_t)c, r);
-            tmem_ld_wait();
-          } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) r[k] = 0u;
-          }
-          if (q == npan - 1 && c + 8 >= C::COLS) {  // this warp is done with the accumulator buffer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[buf]));
-          }
+          for (int k = 0; k < 8; ++k) r[k] = ra[c + k];
           if (p.worker_partials != nullptr && n < p.N) {
             uint32_t* w = reinterpret_cast<uint32_t*>(p.worker_partials) + ((size_t)i * kTile + m0) * p.N + n;
 #pragma unroll
@@ -918,20 +923,20 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             // the accumulator is cleared for the next launch
             int32_t* src = split_partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
                            (quad * 32 + lane);
+            uint32_t rl[C::COLS];
+#pragma unroll
+            for (int k = 0; k < C::COLS; ++k)
+              rl[k] = (uint32_t)(peers ? __ldcv(src + k * kPanelN) : __ldcg(src + k * kPanelN));
+#pragma unroll
+            for (int k = 0; k < C::COLS; ++k) src[k * kPanelN] = 0;
 #pragma unroll
             for (int c = 0; c < C::COLS; c += 16) {
-              uint32_t r[16];
-#pragma unroll
-              for (int k = 0; k < 16; ++k)
-                r[k] = (uint32_t)(peers ? __ldcv(src + (c + k) * kPanelN) : __ldcg(src + (c + k) * kPanelN));
-#pragma unroll
-              for (int k = 0; k < 16; ++k) src[(c + k) * kPanelN] = 0;
               if (od.acc_out != nullptr && n < od.N) {
                 uint32_t* a = reinterpret_cast<uint32_t*>(od.acc_out) + ((size_t)s.row * kTile + m_first + c) * od.N + n;
 #pragma unroll
-                for (int k = 0; k < 16; ++k) a[(size_t)k * od.N] = r[k];
+                for (int k = 0; k < 16; ++k) a[(size_t)k * od.N] = rl[c + k];
               }
-              finish16<KIND>(od2, s.row, n, m_first + c, r, rs, csq, biasq);
+              finish16<KIND>(od2, s.row, n, m_first + c, &rl[c], rs, csq, biasq);
             }
           }
         }

@@ -7,11 +7,12 @@ void_tensor_to_fp8 (:749-766).
 
 What differs from the reference, and why: its kernel converts the FP8 tile to fp32, multiplies it
 by the block's scale and runs an fp32 dot against a floating-point B (:638-659).  On B200 the
-product runs on the FP8 tensor cores (tcgen05 kind::f8f6f4), which need BOTH operands in FP8, so B
-is E4M3 as well with one scale per column; each tile's fp32 product is multiplied by that tile's
-scale before it is added (the same per-tile order as :646), and the column scales of B are applied
-once in the epilogue (they factor out of the sum).  A floating-point B handed to void_spmm_fp8 is
-quantised per column on the fly.
+FP8 product runs on the FP8 tensor cores (tcgen05 kind::f8f6f4), which need BOTH operands in FP8, so it
+takes B as E4M3 with one scale per column (quantize_cols_fp8); the column scales are applied once in
+the epilogue (they factor out of the sum), A's per-tile scales either folded into A when it is packed
+or applied to every tile's fp32 product (scale_terms of void_spmm_fp8).  A floating-point B handed to
+void_spmm_fp8 stays in floating point as in the reference: the tiles are dequantised once and the
+floating-point kernel runs.
 """
 from dataclasses import dataclass, field
 from enum import Enum
@@ -269,8 +270,9 @@ def void_spmm_fp8(a: FP8VOIDTensor, b: torch.Tensor, output_dtype: torch.dtype =
                   scale_terms: Optional[int] = None) -> torch.Tensor:
     """FP8 sparse-dense product C = A @ B (void/fp8.py:674-742).
 
-    a: FP8VOIDTensor [M, K];  b: [K, N], either float8_e4m3fn with ``b_scale`` = per-column scales
-    [N], or floating point (then quantised to E4M3 per column here).  Returns [M, N] in
+    a: FP8VOIDTensor [M, K];  b: [K, N], either float8_e4m3fn with ``b_scale`` = per-column scales [N]
+    (quantize_cols_fp8; the FP8 tensor-core product), or floating point as in the reference (then A's tiles are
+    dequantised and the floating-point kernel multiplies them with B as it is).  Returns [M, N] in
     ``output_dtype`` (default float16, as in the reference).
 
     ``scale_terms`` says how the per-tile scales of A (void/fp8.py:638-646) enter the sum:
@@ -290,10 +292,24 @@ def void_spmm_fp8(a: FP8VOIDTensor, b: torch.Tensor, output_dtype: torch.dtype =
         raise NotImplementedError("void_b200 implements E4M3 only")
     M, K = a.shape
     N = b.shape[1]
-    if b.dtype == torch.float8_e4m3fn:
-        b8, col_scale = b, (None if b_scale is None else b_scale.reshape(-1))
-    else:
-        b8, col_scale, _ = quantize_cols_fp8(b)
+    if b.dtype != torch.float8_e4m3fn:
+        # B in floating point stays in floating point, as in the reference kernel (void/fp8.py:648-659: the tile
+        # is dequantised, B is loaded as it is, tl.dot multiplies them as TF32): the tiles are dequantised once
+        # (cached on the tensor) and the floating-point kernel runs - TF32 for an fp32 B, exact 16-bit products
+        # when B is fp16 / bf16.  The FP8 tensor-core product needs B in E4M3: pass quantize_cols_fp8(b) for that.
+        from .ops import void_spmm
+        if b_scale is not None:
+            raise ValueError("b_scale belongs to an FP8 B")
+        dt = b.dtype if b.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        cache = a.__dict__.setdefault("_dequantised", {})
+        key = (a.values_fp8.data_ptr(), a.values_fp8._version, a.scaling_info.scale.data_ptr(), a.scaling_info.scale._version)
+        hit = cache.get(dt)
+        if hit is None or hit[0] != key:
+            hit = cache[dt] = (key, a.to_void_tensor(dt))
+        if out is None:
+            out = torch.empty(M, N, dtype=output_dtype, device=b.device)
+        return void_spmm(hit[1], b if b.dtype == dt else b.to(dt), out, activation=activation, bias=bias)
+    b8, col_scale = b, (None if b_scale is None else b_scale.reshape(-1))
     if out is None:
         out = torch.empty(M, N, dtype=output_dtype, device=b.device)
     if scale_terms is None:
