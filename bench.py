@@ -104,6 +104,7 @@ def parse_args():
     ap.add_argument("--sparsity", type=float, default=0.9)
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-depth", type=int, default=4, help="steps in flight in the end-to-end leg")
     ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling record of a multi-GPU run")
     ap.add_argument("--copies", type=int, default=0, help="distinct input copies to rotate over (0 = enough for L2)")
     return ap.parse_args()
@@ -680,7 +681,7 @@ def main():
     # pipeline of three steps in flight on three streams (copy-in, operator, copy-out; a serving
     # loop: throughput).  Each step of the pipeline still moves its own inputs and result.
     a_e, bq_e, bs_e, out_e = sets[0]
-    DEPTH = 3
+    DEPTH = max(1, args.e2e_depth)
     slots = []
     for _ in range(DEPTH):
         h_b = torch.empty(bq_e.view(torch.uint8).shape, dtype=torch.uint8).pin_memory()
