@@ -338,7 +338,12 @@ typedef struct void_spmm_args {
    * scratch, e.g. by a small collective on the stream).  Row-accumulate kernel only, not with transposed,
    * acc_out or worker_partials.                                                                        */
   int32_t n_peers;
-  int32_t reserved2;
+  /* 1: instead of adding into one shared accumulator per row, every contributing rank STORES its int32 partial tile
+   * into its own slot of the owner's scratch - peer_partials[owner] + ((counter * n_peers + this rank) * panels_per_item
+   * + panel) * 16 KiB - with plain stores and nothing else (no counters, no last arriver; peer_counters / peer_out are
+   * not used; a rank without tiles in a row stores nothing).  The owner adds the slots and dequantises with
+   * void_reduce_slots once every rank's launch has finished.  partials_bytes = size of one rank's slot array.  */
+  int32_t peer_slots;
   void* peer_partials[8];
   int32_t* peer_counters[8];
   void* peer_out[8];
@@ -422,6 +427,19 @@ VOID_API int void_spmm_i8_static_scratch(const void_spmm_args* args, int32_t n_s
  * a stream of such launches costs per launch is the part of an SpMM launch's time that no kernel code can
  * remove; bench.py --workload floor reports it next to an SpMM over an empty A. */
 VOID_API int void_launch_floor(int32_t grid, int32_t threads, int32_t smem_bytes, void_stream_t stream);
+
+/* Second half of the sum over ranks in slot form (void_spmm_args.peer_slots): for the rows_owned tile rows this
+ * GPU owns (global tile rows row0 ...), add the partial tiles the ranks stored - slots [rows_owned][chunk][n_ranks][panel of the
+ * chunk][32][128] int32 with chunks of panels_per_item panels as in the SpMM launch, contrib[row] = bit mask of the
+ * ranks that stored one - and apply the INT8 epilogue of
+ * void/int_quant.py:516-540 with the WHOLE row's mean scale (row_scale, indexed by global tile row), per-column
+ * scales, bias and activation; out = this GPU's rows of C, [rows_owned * 32, N].  Together with the stores of the
+ * SpMM launches this replaces dist.all_reduce of the full result, void/distributed.py:252-267. */
+VOID_API int void_reduce_slots(const void* slots, const uint8_t* contrib, int32_t n_ranks, int32_t rows_owned,
+                               int32_t row0, int32_t n_panels, int32_t panels_per_item, const float* row_scale,
+                               const float* col_scale,
+                               float b_scale, const float* bias, int32_t act, void* out, int64_t ldc,
+                               int32_t out_dtype, int32_t M, int32_t N, void_stream_t stream);
 
 /* number of SMs of the current device (grid sizing on the host side) */
 VOID_API int void_device_sm_count(void);

@@ -85,13 +85,15 @@ def test_sharded_generator_matches_global_mask():
     assert np.array_equal(np.diff(rp.cpu().numpy()), mask[64:96].sum(axis=1))
 
 
+@pytest.mark.parametrize("mode", ["slots", "atomic"])
 @pytest.mark.parametrize("strategy", [void.ShardingStrategy.COLUMN_WISE, void.ShardingStrategy.BLOCK_WISE])
 @pytest.mark.parametrize("world", [2, 3])
-def test_in_kernel_reduction_bookkeeping_on_one_gpu(strategy, world):
+def test_in_kernel_reduction_bookkeeping_on_one_gpu(strategy, world, mode):
     """The cross-rank reduction of the SpMM kernel with every "rank" played by this one GPU, one launch after the
-    other: each launch adds its int32 partial tiles into the owner's accumulator and bumps the owner's counter, the
-    last one finishes the row.  The owners' rows together must be the unsharded product bit for bit, in any launch
-    order, and accumulators and counters must be left at zero."""
+    other.  "atomic": each launch adds its int32 partial tiles into the owner's accumulator and bumps the owner's
+    counter, the last one finishes the row; accumulators and counters must be left at zero.  "slots": each launch
+    stores its partial tiles into its own slot of the owner's scratch and the owner adds the slots afterwards.
+    Either way the owners' rows together must be the unsharded product bit for bit, in any launch order."""
     from void_b200 import reduce as vr
     mask = workloads.uniform_mask(22, 19, 0.7, seed=12)
     mask[5] = False                                              # a tile row nobody holds a tile of
@@ -99,34 +101,52 @@ def test_in_kernel_reduction_bookkeeping_on_one_gpu(strategy, world):
     q = void.quantize_void_tensor(w.a)
     bq, bs = void.quantize_cols_int8(w.b)
     M, N = q.shape[0], 320
+    slots = mode == "slots"
     for out_dtype in (torch.float16, torch.float32):
         full = void.void_spmm_int8(q, bq, bs, out_dtype=out_dtype)
         shards = [void.shard_void_tensor(q, strategy, world, r) for r in range(world)]
         assert sum(d.n_local_blocks for d in shards) == q.n_blocks
         states, bufs = [], []
         for d in shards:
-            st0 = vr.build_state(d, N, out_dtype, scratch=vr.Scratch(torch.zeros(1, dtype=torch.uint8, device="cuda"), [0], 0, 0, 0))
+            st0 = vr.build_state(d, N, out_dtype, mode=mode,
+                                 scratch=vr.Scratch(torch.zeros(1, dtype=torch.uint8, device="cuda"), [0], 0, 0, 0))
             rows_max = max(e - s for s, e in st0.ranges)
-            acc, ctr_off, out_off, total = vr._layout(rows_max, st0.n_chunks, st0.np, N, full.element_size())
+            acc, ctr_off, out_off, total = vr._layout(rows_max, st0.n_chunks, st0.np, N, full.element_size(), world if slots else 0)
             buf = torch.zeros(total, dtype=torch.uint8, device="cuda")
-            st0.scratch = vr.Scratch(buf, [], acc, ctr_off, out_off)
+            st0.scratch = vr.Scratch(buf, [], acc, ctr_off, out_off, None, slots)
             states.append(st0)
             bufs.append(buf)
         ptrs = [b_.data_ptr() for b_ in bufs]
-        for order in (list(range(world)), list(reversed(range(world)))):
-            for b_ in bufs:
-                b_[states[0].scratch.out_off:].fill_(0xFF)        # stale rows of C must be overwritten
-            for r in order:
-                vr.launch_reduce(states[r], bq, bs, 1.0, ptrs, world)
-            torch.cuda.synchronize()
-            void.check_device_status()
+        # which ranks hold tiles of which tile row (what contributors() gathers over the process group)
+        contrib_all = torch.zeros(states[0].packed.nbr, dtype=torch.int32, device="cuda")
+        for r, st0 in enumerate(states):
+            contrib_all |= ((st0.packed.row_ptr[1:] - st0.packed.row_ptr[:-1]) > 0).to(torch.int32) << r
+        contrib_all = contrib_all.to(torch.uint8)
+        for call, order in enumerate((list(range(world)), list(reversed(range(world))))):
             sc = states[0].scratch
             parts = []
-            for r, (s, e) in enumerate(states[0].ranges):
-                rows = max(min(e * 32, M) - s * 32, 0)
-                parts.append(bufs[r][sc.out_off: sc.out_off + rows * N * full.element_size()].view(out_dtype).view(rows, N))
-                assert not bufs[r][:sc.out_off].any()               # accumulators and counters back at zero
-            assert torch.equal(torch.cat(parts), full), (strategy, world, out_dtype, order)
+            if slots:
+                for b_ in bufs:
+                    b_[call * sc.acc_bytes:(call + 1) * sc.acc_bytes].fill_(0x5A)   # stale slots must not matter where a rank contributes
+                for r in order:
+                    vr.launch_reduce(states[r], bq, None, 1.0, ptrs, world, slot_set=call)
+                for r, (s, e) in enumerate(states[0].ranges):
+                    out_r = torch.full((max(e - s, 0) * 32, N), float("nan"), dtype=out_dtype, device="cuda")
+                    vr.reduce_owned_rows(states[r], ptrs[r] + call * sc.acc_bytes, contrib_all[s:e].contiguous(), r, world, bs, 1.0, out_r)
+                    parts.append(out_r[:max(min(e * 32, M) - s * 32, 0)])
+            else:
+                for b_ in bufs:
+                    b_[sc.out_off:].fill_(0xFF)                   # stale rows of C must be overwritten
+                for r in order:
+                    vr.launch_reduce(states[r], bq, bs, 1.0, ptrs, world)
+                for r, (s, e) in enumerate(states[0].ranges):
+                    rows = max(min(e * 32, M) - s * 32, 0)
+                    parts.append(bufs[r][sc.out_off: sc.out_off + rows * N * full.element_size()].view(out_dtype).view(rows, N))
+                    torch.cuda.synchronize()
+                    assert not bufs[r][:sc.out_off].any()           # accumulators and counters back at zero
+            torch.cuda.synchronize()
+            void.check_device_status()
+            assert torch.equal(torch.cat(parts), full), (strategy, world, out_dtype, order, mode)
 
 
 def test_sharded_workload_shape_vs_oracle():

@@ -52,6 +52,10 @@ def _worker(rank, world, port, ret):
                     full = void.distributed_void_spmm(d, bq, b_scale=bs, out_dtype=out_dtype)
                     assert full.shape == want.shape and torch.equal(full, want), (strategy, out_dtype, "gathered")
                     shard = void.distributed_void_spmm(d, bq, b_scale=bs, out_dtype=out_dtype, gather_output=False)
+                    if strategy != void.ShardingStrategy.ROW_WISE:      # the single-kernel form with atomic adds as well
+                        from void_b200.reduce import fused_reduce_spmm
+                        again = fused_reduce_spmm(d, bq, bs, out_dtype, mode="atomic")
+                        assert torch.equal(again, shard), (strategy, out_dtype, "atomic form")
                     s, e = d.owner_ranges()[rank]
                     rows = min(e * 32, q.shape[0]) - s * 32
                     assert torch.equal(shard[:rows], want[s * 32:s * 32 + rows]), (strategy, out_dtype, "shard")

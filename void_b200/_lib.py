@@ -42,7 +42,7 @@ class SpmmArgs(ctypes.Structure):
         ("partials", c_vp), ("partials_bytes", c_i64), ("counters", c_vp), ("worker_partials", c_vp),
         ("status", c_vp),
         ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
-        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp), ("transposed", c_i32), ("test_hooks", c_i32), ("tile_terms", c_i32), ("reserved", c_i32), ("n_peers", c_i32), ("reserved2", c_i32),
+        ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp), ("transposed", c_i32), ("test_hooks", c_i32), ("tile_terms", c_i32), ("reserved", c_i32), ("n_peers", c_i32), ("peer_slots", c_i32),
         ("peer_partials", c_vp * 8), ("peer_counters", c_vp * 8), ("peer_out", c_vp * 8),
     ]
 
@@ -62,6 +62,8 @@ _PROTOTYPES = {
     "void_csr_scatter": (ctypes.c_int, [c_vp, c_vp, c_vp, c_i32, c_i32, c_vp, c_i64, c_vp, c_vp]),
     "void_pack_tiles": (ctypes.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "void_pack_tiles_f8_split": (ctypes.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "void_reduce_slots": (ctypes.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp, c_vp, c_f32, c_vp, c_i32, c_vp, c_i64,
+                                         c_i32, c_i32, c_i32, c_vp]),
     "void_pack_tiles_fp": (ctypes.c_int, [c_vp, c_i32, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_i8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp]),
     "void_quant_fp8_tiles": (ctypes.c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),

@@ -2,6 +2,8 @@
 // Morton-ordered tiles into tile-row-major core-matrix order, the INT8 / FP8-E4M3 quantisers
 // for A tiles and for the columns of B, and the Stream-K worker table.  All of them are
 // bandwidth-bound elementwise or gather kernels; none waits on another CTA.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -170,6 +172,58 @@ __global__ void pack_tiles_f8_split_kernel(const uint4* __restrict__ values, con
   }
 #pragma unroll
   for (int k = 0; k < TERMS; ++k) packed[(j * TERMS + k) * 64 + q] = make_uint4(out[k][0], out[k][1], out[k][2], out[k][3]);
+}
+
+// Sum of the per-rank partial tiles of the tile rows this GPU owns, then the INT8 epilogue.  One block per
+// (owned tile row, 128-column panel), one thread per column n: the slots hold int32 tiles [32 m][128 n], so a
+// warp reads 128 contiguous bytes per m.  contrib[row] has bit r set when rank r stored a tile for the row
+// (a rank without tiles in the row stores nothing and its slot is not read).
+__device__ __forceinline__ float reduce_act(float x, int act) {
+  if (act == VOID_ACT_RELU) return fmaxf(x, 0.0f);
+  if (act == VOID_ACT_GELU) {
+    const float two_u = 1.5957691216f * x * fmaf(0.044715f * x, x, 1.0f);
+    return x * __fdividef(1.0f, 1.0f + __expf(-two_u));
+  }
+  if (act == VOID_ACT_SILU) return x * __fdividef(1.0f, 1.0f + __expf(-x));
+  return x;
+}
+__global__ void __launch_bounds__(128) reduce_slots_kernel(const int32_t* __restrict__ slots, const uint8_t* __restrict__ contrib,
+                                                           int n_ranks, int rows_owned, int row0, int n_panels,
+                                                           int np, const float* __restrict__ row_scale,
+                                                           const float* __restrict__ col_scale, float b_scale,
+                                                           const float* __restrict__ bias, int act, void* out,
+                                                           long long ldc, int out_dtype, int M, int N) {
+  const int item = blockIdx.x;                 // local row * n_panels + panel
+  const int lr = item / n_panels, pan = item - lr * n_panels;
+  if (lr >= rows_owned) return;
+  const int n = pan * 128 + threadIdx.x;
+  const unsigned mask = contrib[lr];
+  int acc[32];
+#pragma unroll
+  for (int m = 0; m < 32; ++m) acc[m] = 0;
+  for (int r = 0; r < n_ranks; ++r) {
+    if (!((mask >> r) & 1u)) continue;
+    // slots are laid out as the SpMM kernel writes them: [row][chunk of np panels][rank][panel of the chunk]
+    const int n_chunks = (n_panels + np - 1) / np;
+    const int32_t* t = slots + ((((size_t)lr * n_chunks + pan / np) * n_ranks + r) * np + pan % np) * 4096 + threadIdx.x;
+#pragma unroll
+    for (int m = 0; m < 32; ++m) acc[m] += __ldcs(t + m * 128);
+  }
+  if (n >= N) return;
+  const int grow = row0 + lr;                  // global tile row
+  const float rs = row_scale[grow];
+  const float cs = (col_scale != nullptr ? col_scale[n] : 1.0f) * b_scale;
+  const float bi = bias != nullptr ? bias[n] : 0.0f;
+#pragma unroll
+  for (int m = 0; m < 32; ++m) {
+    const long long gm = (long long)grow * 32 + m;
+    if (gm >= M) break;
+    const float v = reduce_act((__int2float_rn(acc[m]) * rs) * cs + bi, act);
+    const size_t o = (size_t)(lr * 32 + m) * ldc + n;
+    if (out_dtype == VOID_OUT_F16) reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
+    else if (out_dtype == VOID_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(out)[o] = v;
+  }
 }
 
 // largest tile scale of every tile row (0 for an empty row)
@@ -497,6 +551,21 @@ int void_pack_tiles_f8_split(const void* values, const float* scales, int64_t n_
                                                            block_rows, block_indices, row_scale, nnz,
                                                            reinterpret_cast<uint4*>(packed));
   }
+  return last_status();
+}
+
+int void_reduce_slots(const void* slots, const uint8_t* contrib, int32_t n_ranks, int32_t rows_owned, int32_t row0,
+                      int32_t n_panels, int32_t panels_per_item, const float* row_scale, const float* col_scale, float b_scale, const float* bias,
+                      int32_t act, void* out, int64_t ldc, int32_t out_dtype, int32_t M, int32_t N, void_stream_t stream) {
+  if (n_ranks < 1 || n_ranks > 8 || rows_owned < 0 || n_panels < 1 || N < 1 || M < 0) return VOID_ERR_BAD_ARG;
+  if (panels_per_item != 1 && panels_per_item != 2 && panels_per_item != 4) return VOID_ERR_BAD_ARG;
+  if (out_dtype < VOID_OUT_F32 || out_dtype > VOID_OUT_BF16 || act < VOID_ACT_NONE || act > VOID_ACT_SILU) return VOID_ERR_BAD_ARG;
+  if (rows_owned == 0) return VOID_OK;
+  if (slots == nullptr || contrib == nullptr || row_scale == nullptr || out == nullptr || ldc < N) return VOID_ERR_BAD_ARG;
+  if ((long long)n_panels * 128 < N) return VOID_ERR_SHAPE;
+  reduce_slots_kernel<<<(unsigned)(rows_owned * n_panels), 128, 0, as_stream(stream)>>>(
+      reinterpret_cast<const int32_t*>(slots), contrib, n_ranks, rows_owned, row0, n_panels, panels_per_item, row_scale, col_scale, b_scale,
+      bias, act, out, ldc, out_dtype, M, N);
   return last_status();
 }
 

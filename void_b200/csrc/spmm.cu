@@ -115,6 +115,8 @@ struct SpmmParams {
   // segment the owner of its tile row; the row's accumulator, arrival counter and rows of C are the owner's,
   // reached through peer pointers (peer_out is offset so that the GLOBAL tile row indexes it).
   int n_peers;
+  int peer_slots;   // 1: every contributing rank stores its partial tile into its own slot of the owner's scratch
+                    // (plain stores, no counters); a second kernel on the owner adds the slots (void_reduce_slots)
   int32_t* peer_partials[8];
   int32_t* peer_counters[8];
   void* peer_out[8];
@@ -873,7 +875,13 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             // (integer adds commute, so the total does not depend on which CTA - or which GPU - comes first)
             int32_t* dst = split_partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m0 * kPanelN +
                            (quad * 32 + lane);
-            if (p.n_peers > 0) {   // the accumulator may be another GPU's: system-wide adds over NVLink
+            if (peers && p.peer_slots) {
+              // this rank's own slot of the row: nothing else writes it, plain stores (NVLink writes for a remote owner)
+              int32_t* slot = split_partials + (((size_t)s.ctr * p.n_peers + s.my_idx) * p.np + q) * (kTile * kPanelN) +
+                              (size_t)m0 * kPanelN + (quad * 32 + lane);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) slot[k * kPanelN] = (int32_t)r[k];
+            } else if (p.n_peers > 0) {   // the accumulator may be another GPU's: system-wide adds over NVLink
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 if (KIND == VOID_KIND_I8) atomicAdd_system(dst + k * kPanelN, (int32_t)r[k]);
@@ -889,7 +897,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
           }
         }
       }
-      if (s.nseg > 1 && !bad_split) {
+      if (s.nseg > 1 && !bad_split && !(peers && p.peer_slots)) {
         // the CTA that arrives last reads the completed sums back and finishes the row
         if (epi_tid == 0) stamp<TRACE>(p, 12);
         if (peers) __threadfence_system(); else __threadfence();
@@ -1337,12 +1345,15 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.worker_partials = reinterpret_cast<int32_t*>(a->worker_partials);
   p.status = a->status;
   p.n_peers = a->n_peers;
+  p.peer_slots = a->peer_slots ? 1 : 0;
   if (a->n_peers < 0 || a->n_peers > 8) return VOID_ERR_BAD_ARG;
+  if (a->peer_slots != 0 && (a->n_peers == 0 || kind != VOID_KIND_I8)) return VOID_ERR_BAD_ARG;
   if (a->n_peers > 0) {
     // reduction across GPUs: a plan whose segments name the owner of their tile row; INT8 / floating row-accumulate
     if (a->segs == nullptr || drain || tr || a->acc_out != nullptr || a->worker_partials != nullptr) return VOID_ERR_BAD_ARG;
     for (int r = 0; r < a->n_peers; ++r) {
-      if (a->peer_partials[r] == nullptr || a->peer_counters[r] == nullptr || a->peer_out[r] == nullptr) return VOID_ERR_BAD_ARG;
+      if (a->peer_partials[r] == nullptr) return VOID_ERR_BAD_ARG;
+      if (!a->peer_slots && (a->peer_counters[r] == nullptr || a->peer_out[r] == nullptr)) return VOID_ERR_BAD_ARG;
       p.peer_partials[r] = reinterpret_cast<int32_t*>(a->peer_partials[r]);
       p.peer_counters[r] = a->peer_counters[r];
       p.peer_out[r] = a->peer_out[r];
@@ -1361,7 +1372,8 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   // room of the split-row scratch, in rows: the kernel refuses segments whose counter index lies beyond it
   p.ctr_limit = 0;
   if (a->segs != nullptr && ((a->partials != nullptr && a->counters != nullptr) || a->n_peers > 0) && a->partials_bytes > 0) {
-    const long long rows = a->partials_bytes / ((long long)np * kPanelN * kTile * (long long)sizeof(int32_t));
+    const long long per_row = (long long)np * kPanelN * kTile * (long long)sizeof(int32_t) * (a->peer_slots ? a->n_peers : 1);
+    const long long rows = a->partials_bytes / per_row;
     p.ctr_limit = rows > 0x7fffffffll ? 0x7fffffff : (int)rows;
   }
   // test hooks (args->test_hooks): bits 0..15 = limit of every device-side wait in milliseconds (0: the

@@ -9,6 +9,16 @@ reads the sums back, dequantises and writes the owner's rows of C.  That is a re
 collective in the data path, and no kernel waits for another GPU.  Integer adds commute, so the result
 is the one-GPU result bit for bit.
 
+Two forms of it are built (``mode`` of fused_reduce_spmm):
+  "slots" (default)  every rank STORES its int32 partial tile into its own slot of the owner's scratch (plain
+                     16 KB tiles over NVLink at copy speed, no atomics, no counters); after the ordering
+                     all_reduce the owner adds the slots of its rows and dequantises (void_reduce_slots, a
+                     bandwidth-bound pass over local memory).  Slots are double-buffered by call parity, so one
+                     all_reduce per call orders everything.
+  "atomic"           the single-kernel form described above (system-scope atomic adds, last arriver finishes);
+                     needs world times less scratch, but 4-byte atomic adds over NVLink run at a quarter of the
+                     copy bandwidth.
+
 Scratch (per rank: int32 accumulators for the rows it owns, their counters, its rows of C) lives in one
 buffer that every rank can address: torch's symmetric memory when it can be set up, else CUDA IPC handles
 of an ordinary allocation.  Consecutive launches are ordered by one small all_reduce on the stream: it ends
@@ -65,9 +75,15 @@ class Scratch:
     ctr_off: int
     out_off: int
     keep: object = None                  # whatever must stay alive for the peer mappings
+    slots: bool = False                  # slot form: acc_bytes is the size of ONE of the two slot sets
 
 
-def _layout(rows_max: int, n_chunks: int, np_: int, N: int, out_bytes: int):
+def _layout(rows_max: int, n_chunks: int, np_: int, N: int, out_bytes: int, slot_ranks: int = 0):
+    """Offsets inside a rank's scratch.  Atomic form: accumulators, counters, the rank's rows of C.  Slot form
+    (slot_ranks = world size): two sets of per-rank slots, nothing else."""
+    if slot_ranks:
+        one = rows_max * n_chunks * slot_ranks * np_ * PANEL * TILE * 4
+        return one, 2 * one, 2 * one, 2 * one
     acc = rows_max * n_chunks * np_ * PANEL * TILE * 4
     ctr_off = (acc + 255) // 256 * 256
     out_off = (ctr_off + rows_max * n_chunks * 4 + 255) // 256 * 256
@@ -137,10 +153,13 @@ class ReduceState:
     ranges: Tuple[Tuple[int, int], ...]
     scratch: Scratch
     token: torch.Tensor                  # the word the ordering all_reduce adds up
+    contrib: Optional[torch.Tensor] = None    # slot form: uint8 per owned tile row, bit r = rank r holds tiles of the row
+    out: Optional[torch.Tensor] = None        # slot form: this rank's rows of C (ordinary memory)
+    calls: int = 0                            # slot form: parity selects the slot set
 
 
 def launch_reduce(state: ReduceState, b: torch.Tensor, col_scale: Optional[torch.Tensor], b_scalar: float,
-                  scratch_ptrs: Sequence[int], rank_count: int, act: int = 0, bias=None) -> None:
+                  scratch_ptrs: Sequence[int], rank_count: int, act: int = 0, bias=None, slot_set: int = 0) -> None:
     """One reducing launch on the current stream: void_spmm_i8 with n_peers = rank_count and, per owner rank,
     the addresses of its accumulators, counters and rows of C inside the buffer ``scratch_ptrs[owner]``."""
     import ctypes
@@ -174,8 +193,9 @@ def launch_reduce(state: ReduceState, b: torch.Tensor, col_scale: Optional[torch
     a.panels_per_item = state.np
     a.flags = _spmm.FLAG_A_STABLE if pk.is_stable() else 0
     a.n_peers = rank_count
+    a.peer_slots = 1 if sc.slots else 0
     for r in range(rank_count):
-        base = scratch_ptrs[r]
+        base = scratch_ptrs[r] + (slot_set * sc.acc_bytes if sc.slots else 0)
         a.peer_partials[r] = base
         a.peer_counters[r] = base + sc.ctr_off
         # the owner's rows of C, moved back by its first row so that the global tile row indexes it
@@ -184,8 +204,17 @@ def launch_reduce(state: ReduceState, b: torch.Tensor, col_scale: Optional[torch
         _lib.check(lib.void_spmm_i8(ctypes.byref(a), _lib.stream_ptr(dev)), "void_spmm_i8 (reduce)")
 
 
+def contributors(row_ptr: torch.Tensor, rank: int, group=None) -> torch.Tensor:
+    """uint8 per tile row of the whole matrix: bit r set when rank r holds at least one tile of the row
+    (every rank knows its own rows; the masks are added up over the ranks - the bits are distinct)."""
+    mine = ((row_ptr[1:] - row_ptr[:-1]) > 0).to(torch.int32) << rank
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(mine, group=group)
+    return mine.to(torch.uint8)
+
+
 def build_state(dist_tensor, N: int, out_dtype: torch.dtype, group=None, n_cta: Optional[int] = None,
-                scratch: Optional[Scratch] = None) -> ReduceState:
+                scratch: Optional[Scratch] = None, mode: str = "slots") -> ReduceState:
     """Pack the local tiles against the GLOBAL shape, build the plan and (unless given) the shared scratch."""
     from .int_quant import Int8VOIDTensor
     local = dist_tensor.local_tensor
@@ -193,11 +222,13 @@ def build_state(dist_tensor, N: int, out_dtype: torch.dtype, group=None, n_cta: 
         raise NotImplementedError("the reducing SpMM is built for Int8VOIDTensor shards (integer sums commute)")
     if dist_tensor.world_size > MAX_PEERS:
         raise ValueError("at most %d ranks" % MAX_PEERS)
+    if mode not in ("slots", "atomic"):
+        raise ValueError("mode must be 'slots' or 'atomic'")
     if dist_tensor.global_row_scale is None:
         raise ValueError("shard the tensor with shard_void_tensor on its CUDA device: the mean tile scale of whole rows is needed")
     dev = local.values.device
     M, K = dist_tensor.global_shape
-    nbr = (M + TILE - 1) // TILE
+    world, rank = dist_tensor.world_size, dist_tensor.rank
     packed = _spmm.pack(local.values, local.scales, local.block_rows, local.block_cols, (M, K), _lib.KIND_I8)
     packed.row_scale = dist_tensor.global_row_scale.to(device=dev, dtype=torch.float32).contiguous()
     packed = _spmm._mark_ready(packed)
@@ -206,41 +237,85 @@ def build_state(dist_tensor, N: int, out_dtype: torch.dtype, group=None, n_cta: 
     np_ = 2 if panels >= 2 else 1
     n_chunks = (panels + np_ - 1) // np_
     ranges = tuple(dist_tensor.owner_ranges())
-    segs, cta_seg_ptr, n_cta = reduce_segments(packed.row_ptr, n_chunks, dist_tensor.world_size, dist_tensor.rank, ranges,
-                                               n_cta or 4 * sms)
+    segs, cta_seg_ptr, n_cta = reduce_segments(packed.row_ptr, n_chunks, world, rank, ranges, n_cta or 4 * sms)
     rows_max = max(e - s for s, e in ranges)
     elem = torch.empty(0, dtype=out_dtype).element_size()
-    acc, ctr_off, out_off, total = _layout(rows_max, n_chunks, np_, N, elem)
-    if scratch is None:
+    slots = mode == "slots" and world > 1      # a single rank has nothing to add up: its rows are finished in the launch
+    acc, ctr_off, out_off, total = _layout(rows_max, n_chunks, np_, N, elem, world if slots else 0)
+    made_here = scratch is None
+    if made_here:
         buf, ptrs, keep = shared_buffer(total, dev, group)
-        scratch = Scratch(buf, ptrs, acc, ctr_off, out_off, keep)
-        torch.cuda.synchronize(dev)                      # zeroed everywhere before anybody adds into it
-        if dist.is_initialized() and dist_tensor.world_size > 1:
+        scratch = Scratch(buf, ptrs, acc, ctr_off, out_off, keep, slots)
+    contrib = out = None
+    if slots and made_here:
+        s0, e0 = ranges[rank]
+        contrib = contributors(packed.row_ptr, rank, group)[s0:e0].contiguous()
+        out = torch.empty(max(e0 - s0, 0) * TILE, N, dtype=out_dtype, device=dev)
+    if made_here:
+        torch.cuda.synchronize(dev)                      # zeroed everywhere before anybody writes into it
+        if dist.is_initialized() and world > 1:
             dist.barrier(group)
     token = torch.zeros(1, dtype=torch.int32, device=dev)
-    return ReduceState(packed, segs, cta_seg_ptr, n_cta, np_, n_chunks, N, out_dtype, ranges, scratch, token)
+    return ReduceState(packed, segs, cta_seg_ptr, n_cta, np_, n_chunks, N, out_dtype, ranges, scratch, token, contrib, out)
+
+
+def reduce_owned_rows(state: ReduceState, slots_ptr: int, contrib: torch.Tensor, rank: int, world: int, col_scale, b_scalar: float,
+                      out: torch.Tensor, act: int = 0, bias=None) -> torch.Tensor:
+    """Slot form, second half: add the per-rank partial tiles of this rank's rows (void_reduce_slots)."""
+    lib = _lib.load()
+    dev = out.device
+    s0, e0 = state.ranges[rank]
+    M = state.packed.shape[0]
+    panels = (state.N + PANEL - 1) // PANEL
+    keep = []
+    if col_scale is not None:
+        col_scale = col_scale.to(device=dev, dtype=torch.float32).contiguous()
+        keep.append(col_scale)
+    if bias is not None:
+        bias = bias.to(device=dev, dtype=torch.float32).contiguous()
+        keep.append(bias)
+    import ctypes
+    with torch.cuda.device(dev):
+        _lib.check(lib.void_reduce_slots(ctypes.c_void_p(slots_ptr), _lib.ptr(contrib), world, max(e0 - s0, 0), s0, panels, state.np,
+                                         _lib.ptr(state.packed.row_scale), _lib.ptr(col_scale), float(b_scalar), _lib.ptr(bias), act,
+                                         _lib.ptr(out), out.stride(0) if out.numel() else state.N, _lib.OUT_DTYPE_CODE[out.dtype], M, state.N,
+                                         _lib.stream_ptr(dev)), "void_reduce_slots")
+    return out
 
 
 def fused_reduce_spmm(dist_tensor, b: torch.Tensor, b_scale=None, out_dtype: Optional[torch.dtype] = None,
-                      group=None, activation: int = 0, bias=None) -> torch.Tensor:
+                      group=None, activation: int = 0, bias=None, mode: str = "slots") -> torch.Tensor:
     """This rank's rows of C = A @ B for an Int8 tensor sharded COLUMN_WISE or BLOCK_WISE: [(end - start) * 32, N]
-    for the rank's range of DistributedVOIDTensor.owner_ranges().  The returned tensor is a view of the shared
-    scratch: it is overwritten by the next call on the same sharded tensor.  Every rank must make the same calls."""
+    for the rank's range of DistributedVOIDTensor.owner_ranges().  The returned tensor belongs to the sharded
+    tensor's state: it is overwritten by the next call on it.  Every rank must make the same calls."""
     from .int_quant import _resolve_b
     out_dtype = out_dtype or torch.float32
     N = b.shape[1]
     b_q, scalar, col_scale = _resolve_b(b, b_scale)
-    key = (N, out_dtype)
+    key = (N, out_dtype, mode)
     cache = dist_tensor.__dict__.setdefault("_reduce_states", {})
     st = cache.get(key)
     if st is None:
-        st = cache[key] = build_state(dist_tensor, N, out_dtype, group)
-    launch_reduce(st, b_q, col_scale, scalar, st.scratch.ptrs, dist_tensor.world_size, activation, bias)
-    if dist.is_initialized() and dist_tensor.world_size > 1:
+        st = cache[key] = build_state(dist_tensor, N, out_dtype, group, mode=mode)
+    world, rank = dist_tensor.world_size, dist_tensor.rank
+    multi = dist.is_initialized() and world > 1
+    sc = st.scratch
+    if sc.slots:
+        which = st.calls & 1
+        st.calls += 1
+        # activation and bias belong to the finished sums: the SpMM launches only store raw partial tiles
+        launch_reduce(st, b_q, None, 1.0, sc.ptrs, world, 0, None, slot_set=which)
+        if multi:
+            dist.all_reduce(st.token, group=group)       # ends when every rank's launch has ended: the slots are complete
+        reduce_owned_rows(st, sc.ptrs[rank] + which * sc.acc_bytes, st.contrib, rank, world, col_scale, scalar, st.out,
+                          activation, bias)
+        s, e = st.ranges[rank]
+        return st.out[:max(min(e * TILE, dist_tensor.global_shape[0]) - s * TILE, 0)]
+    launch_reduce(st, b_q, col_scale, scalar, sc.ptrs, world, activation, bias)
+    if multi:
         # ends when every rank's kernel has ended: this rank's rows are complete, and the scratch may be used again
         dist.all_reduce(st.token, group=group)
-    s, e = st.ranges[dist_tensor.rank]
+    s, e = st.ranges[rank]
     rows = min(e * TILE, dist_tensor.global_shape[0]) - s * TILE if e > s else 0
-    sc = st.scratch
     elem = torch.empty(0, dtype=out_dtype).element_size()
     return sc.buffer[sc.out_off: sc.out_off + max(rows, 0) * N * elem].view(out_dtype).view(max(rows, 0), N)
