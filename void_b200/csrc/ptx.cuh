@@ -89,18 +89,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(m), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
-// Hints to the copy engine: bring a box of a tensor / a linear range into L2.  Nothing waits on them
-// and nothing is written; a box outside the tensor is legal (it reads nothing).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int32_t x, int32_t y, int32_t z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(m), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 // Tiled store shared -> global (bulk-group completion).  Rows and columns of the box outside the tensor are
 // not written.  Shared-memory writes made with ordinary stores must be fenced for the async proxy first.
 __device__ __forceinline__ void fence_proxy_async_smem() {

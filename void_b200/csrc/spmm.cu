@@ -28,12 +28,21 @@
 //
 // Two kernels share this pipeline:
 //   spmm_rowacc_kernel  one accumulator per (tile row, column chunk), scaled once by the
-//                       row's mean tile scale (the INT8 semantic of void/int_quant.py:479-526) or
+//                       row's mean tile scale (the INT8 semantic of void/int_quant.py:479-526), by
+//                       the row's reference scale (FP8 tiles packed with their scales folded in: each
+//                       tile is then two or three E4M3 terms that multiply the same panel), or
 //                       not at all (floating point, void/ops.py:93-146); rows cut into several
-//                       segments by a work plan are finished by the CTA that arrives last.
+//                       segments by a work plan are finished by the CTA that arrives last - the
+//                       segments of a row may belong to different GPUs (sum over ranks: partial tiles
+//                       go to the owning rank through peer pointers).
 //   spmm_drain_kernel   every tile's product lands in its own TMEM slot and is folded into
-//                       registers with that tile's scale (the FP8 semantic of
+//                       registers with that tile's scale (the exact FP8 semantic of
 //                       void/fp8.py:638-659; also exact per-block INT8 dequantisation).
+//
+// Launch order: the kernels use programmatic dependent launch.  Set-up touches no global memory; every
+// role then waits for the previous kernel of the stream where it first needs data that kernel may have
+// written.  When the caller vouches that the packed A is not being written by any kernel in flight, the
+// index of A and the first tiles are read ahead of that wait.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cudaTypedefs.h>
