@@ -231,13 +231,13 @@ def build_state(dist_tensor, N: int, out_dtype: torch.dtype, group=None, n_cta: 
     world, rank = dist_tensor.world_size, dist_tensor.rank
     packed = _spmm.pack(local.values, local.scales, local.block_rows, local.block_cols, (M, K), _lib.KIND_I8)
     packed.row_scale = dist_tensor.global_row_scale.to(device=dev, dtype=torch.float32).contiguous()
-    packed = _spmm._mark_ready(packed)
     sms = _spmm.sm_count(dev)
     panels = (N + PANEL - 1) // PANEL
     np_ = 2 if panels >= 2 else 1
     n_chunks = (panels + np_ - 1) // np_
     ranges = tuple(dist_tensor.owner_ranges())
     segs, cta_seg_ptr, n_cta = reduce_segments(packed.row_ptr, n_chunks, world, rank, ranges, n_cta or 4 * sms)
+    packed = _spmm._mark_ready(packed)     # the host waits here: the store AND the plan are complete before any launch reads them early
     rows_max = max(e - s for s, e in ranges)
     elem = torch.empty(0, dtype=out_dtype).element_size()
     slots = mode == "slots" and world > 1      # a single rank has nothing to add up: its rows are finished in the launch
