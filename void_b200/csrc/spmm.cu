@@ -807,9 +807,16 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
               __syncwarp();
             }
             uint16_t* part = stage_tile + quad * (32 * 32);
+            if (!has && p.bias == nullptr && p.row_bias == nullptr) {
+              // an empty tile row without bias is zeros under every activation: 2 KB of zero words, no conversions
+              uint4* z = reinterpret_cast<uint4*>(part) + lane;
 #pragma unroll
-            for (int c = 0; c < C::COLS; c += 16)
-              finish16_stage<KIND, 32>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, part + lane);
+              for (int k = 0; k < 4; ++k) z[k * 32] = make_uint4(0u, 0u, 0u, 0u);
+            } else {
+#pragma unroll
+              for (int c = 0; c < C::COLS; c += 16)
+                finish16_stage<KIND, 32>(od, s.row, n, m_first + c, &r[c], rs, csq, biasq, part + lane);
+            }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
