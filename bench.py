@@ -99,7 +99,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded", "fp32", "fp16", "mid", "floor"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "fp8", "powerlaw", "sharded", "fp32", "fp16", "mid", "floor", "prep"])
     ap.add_argument("--min-timed-ms", type=float, default=50.0, help="repeat the K steps until the timed region lasts this long")
     ap.add_argument("--sparsity", type=float, default=0.9)
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of a CUDA graph")
@@ -324,6 +324,64 @@ def launch_floor(args, torch, void, workloads, _lib, _spmm, dev):
                       "input_copies": ns, "launches_per_graph": 512, **{k: round(v, 3) for k, v in res.items()}}))
 
 
+def prep_kernels(args, torch, void, workloads, _lib, _spmm, dev):
+    """The preparation operators of the path (quantisers, tile index + packing, format build), one after the
+    other on inputs larger than L2, CUDA events around `reps` back-to-back calls of each.  Every figure is the
+    operator's algorithmic bytes (what it must read and write) over its time, against the measured copy peak;
+    an operator is one to four kernels, listed in profiles/prep_kernels.md."""
+    import numpy as np
+    reps = max(1, min(args.steps, 20))
+    peak = measured_peaks()["hbm_gbs"]
+    nb = 512
+    mask = workloads.uniform_mask(nb, nb, 0.85, 0)                  # 39 k tiles: 161 MB of fp32 tile values
+    nnz = int(mask.sum())
+    g = torch.Generator(device="cpu").manual_seed(0)
+    a = workloads.block_sparse(mask, 8, seed=0, device=dev).a
+    b = torch.randn(nb * 32, 2048, generator=g).to(dev)             # 134 MB fp32
+    dense = torch.randn(8192, 8192, generator=g).to(dev) * (torch.rand(256, 256, generator=g) > 0.5).to(dev).repeat_interleave(32, 0).repeat_interleave(32, 1)
+    q = void.quantize_void_tensor(a)
+    a8 = void.void_tensor_to_fp8(a)
+    K, N = b.shape
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    def pack_i8():
+        return _spmm.pack(q.values, q.scales, q.block_rows, q.block_cols, q.shape, _lib.KIND_I8)
+
+    def pack_f8(terms):
+        return _spmm.pack_f8_split(a8.values_fp8.view(torch.uint8), a8.scaling_info.scale, a8.block_rows, a8.block_cols, a8.shape, terms)
+
+    idx = nnz * 12 + (nb + 1) * 4
+    ops = [
+        ("quantize_void_tensor (INT8, per tile)", lambda: void.quantize_void_tensor(a), nnz * (4096 + 1024 + 4)),
+        ("void_tensor_to_fp8 (E4M3, per tile)", lambda: void.void_tensor_to_fp8(a), nnz * (4096 + 1024 + 12)),
+        ("quantize_cols_int8 (B, per column: absmax pass + quantise pass)", lambda: void.quantize_cols_int8(b), K * N * 9 + N * 4),
+        ("quantize_cols_fp8 (B, per column)", lambda: void.quantize_cols_fp8(b), K * N * 9 + N * 8),
+        ("tile index + pack, INT8 (bitmap mark / count / scan / rank, gather, row scales)", pack_i8, nnz * 2048 + 2 * idx),
+        ("tile index + pack, FP8 tiles as two E4M3 terms", lambda: pack_f8(2), nnz * 3072 + 2 * idx),
+        ("dense_to_void 8192^2 fp32, half of the tiles kept (mark, Morton rank, gather)", lambda: void.dense_to_void(dense),
+         dense.numel() * 4 * 2 + (dense.numel() // 2) * 4),
+        ("compute_stream_k_workload + plan (O(tile rows): latency bound)", lambda: void.compute_stream_k_workload(q), 0),
+    ]
+    res = []
+    for name, fn, nbytes in ops:
+        us = timed(fn)
+        gbs = nbytes / (us * 1e-6) / 1e9 if nbytes else None
+        res.append({"op": name, "us": round(us, 1), "algorithmic_mb": round(nbytes / 1e6, 1),
+                    "gbs": None if gbs is None else round(gbs), "frac_of_measured_hbm": None if gbs is None else round(gbs / peak, 3)})
+    _lib.check_device_status(dev)
+    print(json.dumps({"workload": "prep", "tiles": nnz, "b": [K, N], "reps": reps, "hbm_peak_gbs": peak, "ops": res}))
+
+
 def strong_scaling_record(torch, dist, void, workloads, _lib, dev, rank, world):
     """The multi-GPU workload, measured in the same run as the weak-scaling line: A 65536 x 65536 at 95 % block
     sparsity, INT8 per block, B 65536 x 1024 INT8 per column, fp16 row shards.  Total work is fixed:
@@ -542,9 +600,9 @@ def main():
     if args.gpus != world and rank == 0:
         print("bench.py: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE" % (args.gpus, world), file=sys.stderr)
 
-    if args.workload == "floor":
+    if args.workload in ("floor", "prep"):
         if rank == 0:
-            launch_floor(args, torch, void, workloads, _lib, _spmm, dev)
+            (launch_floor if args.workload == "floor" else prep_kernels)(args, torch, void, workloads, _lib, _spmm, dev)
         return
     sampler = ClockSampler(local_rank)
     sampler.start()
