@@ -46,6 +46,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Additions to global memory whose old value nobody reads (no reply travels back), and the arrival count of a
+// split tile row: an add that releases this thread's earlier writes - and, after a barrier, those of the threads
+// that met it there - and acquires what earlier arrivers released.
+__device__ __forceinline__ void red_add_s32(int32_t* p, int32_t v) {
+  asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_f32(float* p, float v) {
+  asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ int atom_add_acq_rel(int32_t* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
+// One lane of the (converged) warp: the lane that issues the single-thread instructions of a warp-wide loop.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " elect.sync _|p, 0xffffffff;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Every device-side wait has a wall-clock limit.  `ctl` points at two shared-memory words every role of the
 // CTA polls: ctl[0] is the abort flag, ctl[1] the limit in milliseconds (kDefaultWaitLimitMs unless the launch
 // asked for another).  A wait that runs out sets the abort flag and returns false; the kernel then drains and

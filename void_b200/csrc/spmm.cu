@@ -555,6 +555,13 @@ __device__ __forceinline__ void pipeline_setup(const SpmmParams& p, const CUtens
                                                uint32_t* tmem_base_s, int* ctl_s, int n_acc, uint32_t tmem_cols) {
   const int warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) stamp<TRACE>(p, 62);
+  if constexpr (TRACE) {   // slot 63: the SM this CTA runs on
+    if (threadIdx.x == 0 && p.trace != nullptr) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      p.trace[(size_t)blockIdx.x * 64 + 63] = smid;
+    }
+  }
   if (threadIdx.x == 0) {
     ctl_s[0] = 0;
     ctl_s[1] = p.wait_limit_ms;
@@ -637,12 +644,15 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     producer_loop<C, ES, TR, TRACE>(p, &tmap_b, &bars, ring_base, stage_bytes, ctl, lane, warp);
     if (warp == 0 && lane == 0) stamp<TRACE>(p, 2);
   } else if (warp == C::MMA) {
-    if (lane == 0) {
-      // This thread reads the index of A and the plan only; everything else reaches it through the ring.
+    {
+      // The whole warp walks the loop and waits on the barriers together; one elected lane issues the MMAs and
+      // the commits.  The control flow stays convergent, so the addresses, descriptors and counters are the
+      // same in every lane and the compiler may keep them in the warp's uniform registers, where the
+      // instruction operands have to be: a loop run by a single lane computes them per thread and moves them
+      // over before every MMA.
+      // The warp reads the index of A and the plan only; everything else reaches it through the ring.
+      const bool leader = elect_one();
       if (!p.a_stable) grid_dependency_wait();
-      // Everything an MMA needs is kept in registers and advanced by constants: this thread runs
-      // alone on its scheduler, so every dependent instruction between two MMAs costs its full
-      // latency.
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
       const int G = p.group, S = p.stages, np = p.np, terms = p.terms;
@@ -666,7 +676,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (i + step < end) seg_next = load_seg(p, i + step);
         const int npan = panels_in_chunk(p, s.chunk);
         const uint32_t buf = it & 1u, aph = (it >> 1) & 1u;
-        ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, ctl);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, ctl));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * acc_cols;
@@ -674,10 +684,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         int gidx = 0;
         for (int t = s.t0; t < s.t1; t += G, ++gidx) {
           const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-          if (TRACE && i == begin && gidx < 8) stamp<TRACE>(p, 48 + gidx);
-          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, ctl);
+          if (TRACE && leader && i == begin && gidx < 8) stamp<TRACE>(p, 48 + gidx);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[stage]), phase, ctl));
           if (!ok) break;
-          if (TRACE && i == begin && gidx < 16) stamp<TRACE>(p, 16 + gidx);
+          if (TRACE && leader && i == begin && gidx < 16) stamp<TRACE>(p, 16 + gidx);
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
           uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
@@ -685,13 +695,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             uint64_t adq = ad;
             uint32_t d = d0;
             for (int q = 0; q < npan; ++q) {
-              issue_mma<KIND>(d, adq, bd, idesc, acc);
+              if (leader) issue_mma<KIND>(d, adq, bd, idesc, acc);
 #pragma unroll
               for (int kk = 1; kk < ES; ++kk)
-                issue_mma<KIND>(d, adq + kk * kPanelKStep, bd + kk * kTileKStep, idesc, 1u);
+                if (leader) issue_mma<KIND>(d, adq + kk * kPanelKStep, bd + kk * kTileKStep, idesc, 1u);
               // a tile stored as a sum of terms: every further term multiplies the same panel
               if (KIND == VOID_KIND_F8E4M3)
-                for (int u = 1; u < terms; ++u) issue_mma<KIND>(d, adq, bd + (uint64_t)u * kTileStep, idesc, 1u);
+                for (int v = 1; v < terms; ++v)
+                  if (leader) issue_mma<KIND>(d, adq, bd + (uint64_t)v * kTileStep, idesc, 1u);
               adq += kPanelStep;
               d += 32u;
             }
@@ -699,16 +710,18 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             bd += kTileStep * (uint64_t)terms;
             acc = 1u;
           }
-          tc_commit(smem_u32(&bars.empty[stage]));
+          if (leader) tc_commit(smem_u32(&bars.empty[stage]));
           sbase += stage_bytes;
           if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
         if (!ok) break;
-        if (s.t1 > s.t0) tc_commit(smem_u32(&bars.acc_full[buf]));
-        else mbar_arrive(smem_u32(&bars.acc_full[buf]));
-        if (i == begin) stamp<TRACE>(p, 3);
+        if (leader) {
+          if (s.t1 > s.t0) tc_commit(smem_u32(&bars.acc_full[buf]));
+          else mbar_arrive(smem_u32(&bars.acc_full[buf]));
+          if (i == begin) stamp<TRACE>(p, 3);
+        }
       }
-      stamp<TRACE>(p, 4);
+      if (leader) stamp<TRACE>(p, 4);
     }
     __syncwarp();
   } else {
@@ -906,8 +919,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
             } else {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
-                if (KIND == VOID_KIND_I8) atomicAdd(dst + k * kPanelN, (int32_t)r[k]);
-                else atomicAdd(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
+                if (KIND == VOID_KIND_I8) red_add_s32(dst + k * kPanelN, (int32_t)r[k]);
+                else red_add_f32(reinterpret_cast<float*>(dst) + k * kPanelN, __uint_as_float(r[k]));
               }
             }
           }
@@ -916,11 +929,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       if (s.nseg > 1 && !bad_split && !(peers && p.peer_slots)) {
         // the CTA that arrives last reads the completed sums back and finishes the row
         if (epi_tid == 0) stamp<TRACE>(p, 12);
-        if (peers) __threadfence_system(); else __threadfence();
+        // The arrival is one release-acquire add by one thread after a barrier of the epilogue warps: the barrier
+        // orders every warp's additions before it, the release makes them visible before the count, and the
+        // acquire lets the last arriver - after the second barrier - read what the other CTAs added.
+        if (peers) __threadfence_system();
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_THREADS) : "memory");
         if (epi_tid == 0) stamp<TRACE>(p, 13);
         if (epi_tid == 0) {
-          const int old = peers ? atomicAdd_system(split_counters + s.ctr, 1) : atomicAdd(split_counters + s.ctr, 1);
+          const int old = peers ? atomicAdd_system(split_counters + s.ctr, 1) : atom_add_acq_rel(split_counters + s.ctr, 1);
           const int last = (old == s.nseg - 1) ? 1 : 0;
           if (last) split_counters[s.ctr] = 0;  // left clean for the next launch
           last_s = last;
@@ -931,26 +947,56 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         if (epi_tid == 0) stamp<TRACE>(p, 14);
         if (TRACE && epi_tid == 0 && p.trace != nullptr) p.trace[(size_t)blockIdx.x * 64 + 15] = (unsigned long long)last;
         if (last) {
-          if (peers) __threadfence_system(); else __threadfence();
+          if (peers) __threadfence_system();
+          if (epi_tid == 0) stamp<TRACE>(p, 28);
           OutDesc od2 = od;
           od2.acc_out = nullptr;
           if (peers) od2.out = p.peer_out[s.slot0];   // the owner's rows of C
 #pragma unroll 1
           for (int q = 0; q < npan; ++q) {
             const int n = n_base + q * kPanelN;
-            float csq = p.b_scale, biasq = 0.0f;
-            if (n < p.N) {
-              if (p.col_scale != nullptr) csq = __ldcg(p.col_scale + n) * p.b_scale;
-              if (p.bias != nullptr) biasq = __ldcg(p.bias + n);
+            float csq = cs, biasq = bias;   // the first panel's were read before the accumulator was ready
+            if (q > 0) {
+              csq = p.b_scale; biasq = 0.0f;
+              if (n < p.N) {
+                if (p.col_scale != nullptr) csq = __ldg(p.col_scale + n) * p.b_scale;
+                if (p.bias != nullptr) biasq = __ldg(p.bias + n);
+              }
             }
             // all of this warp's sums of the panel are requested at once (one L2 round trip), then
             // the accumulator is cleared for the next launch
             int32_t* src = split_partials + ((size_t)s.ctr * p.np + q) * (kTile * kPanelN) + (size_t)m_first * kPanelN +
                            (quad * 32 + lane);
             uint32_t rl[C::COLS];
+            if (TRACE && epi_tid == 0 && q == 0) { asm volatile("" ::"f"(csq), "f"(biasq) : "memory"); stamp<TRACE>(p, 29); }
 #pragma unroll
             for (int k = 0; k < C::COLS; ++k)
               rl[k] = (uint32_t)(peers ? __ldcv(src + k * kPanelN) : __ldcg(src + k * kPanelN));
+            if (TRACE && epi_tid == 0 && q == 0) { asm volatile("" ::"r"(rl[0]), "r"(rl[C::COLS - 1]) : "memory"); stamp<TRACE>(p, 30); }
+            if (epi_tid == 0 && q == 0) stamp<TRACE>(p, 31);
+            if (!TR && p.tma_store == 2 && !peers && od.acc_out == nullptr) {
+              // 16-bit outputs leave as in the unsplit case: the warp's 32 x 32 part through shared memory and one tiled store
+              if (store_pending) {
+                if (lane == 0) bulk_wait_read();
+                __syncwarp();
+              }
+              uint16_t* part = stage_tile + quad * (32 * 32);
+#pragma unroll
+              for (int c = 0; c < C::COLS; c += 16)
+                finish16_stage<KIND, 32>(od, s.row, n, m_first + c, &rl[c], rs, csq, biasq, part + lane);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmap_c, stage_u32 + (uint32_t)quad * (32 * 32 * 2), (s.chunk * p.np + q) * kPanelN + quad * 32,
+                             s.row * kTile);
+                bulk_commit();
+              }
+              store_pending = true;
+              // (cleared after the store has been issued: the fence in front of it would wait for these writes)
+#pragma unroll
+              for (int k = 0; k < C::COLS; ++k) src[k * kPanelN] = 0;
+              continue;
+            }
 #pragma unroll
             for (int k = 0; k < C::COLS; ++k) src[k * kPanelN] = 0;
 #pragma unroll
@@ -1012,7 +1058,9 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
     producer_loop<C, 1, false, TRACE>(p, &tmap_b, &bars, ring_base, stage_bytes, ctl, lane, warp);
     if (warp == 0 && lane == 0) stamp<TRACE>(p, 2);
   } else if (warp == C::MMA) {
-    if (lane == 0) {
+    {
+      // as in the row-accumulate kernel: the warp walks the loop together, one elected lane issues
+      const bool leader = elect_one();
       if (!p.a_stable) grid_dependency_wait();
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
@@ -1033,9 +1081,9 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
         const int npan = panels_in_chunk(p, s.chunk);
         for (int t = s.t0; t < s.t1; t += G) {
           const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, ctl);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[stage]), phase, ctl));
           if (!ok) break;
-          ok = mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, ctl);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_empty[slot]), sphase ^ 1u, ctl));
           if (!ok) break;
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
@@ -1045,7 +1093,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
             uint64_t adq = ad;
             uint32_t dq = d;
             for (int q = 0; q < npan; ++q) {
-              issue_mma<KIND>(dq, adq, bd, idesc, 0u);
+              if (leader) issue_mma<KIND>(dq, adq, bd, idesc, 0u);
               adq += kPanelStep;
               dq += 32u;
             }
@@ -1053,14 +1101,16 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
             bd += kTileStep;
             d += kTileCols;
           }
-          tc_commit(smem_u32(&bars.acc_full[slot]));
-          tc_commit(smem_u32(&bars.empty[stage]));
+          if (leader) {
+            tc_commit(smem_u32(&bars.acc_full[slot]));
+            tc_commit(smem_u32(&bars.empty[stage]));
+          }
           if (++slot == n_slots) { slot = 0; sphase ^= 1u; }
           sbase += stage_bytes;
           if (++stage == S) { stage = 0; phase ^= 1u; sbase = ring_base; }
         }
       }
-      stamp<TRACE>(p, 4);
+      if (leader) stamp<TRACE>(p, 4);
     }
     __syncwarp();
   } else {

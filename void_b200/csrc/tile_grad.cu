@@ -132,14 +132,17 @@ __global__ void __launch_bounds__(kThreads, 2) tile_grad_kernel(const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // the warp walks the loop and waits together, one elected lane issues the MMAs and commits: the loop
+      // stays convergent, so descriptors and addresses can live in the warp's uniform registers
+      const bool leader = elect_one();
       const uint32_t idesc = p.idesc;
       const uint64_t hi = p.desc_hi;
       uint32_t g = 0, n = 0;
       bool ok = true;
       for (int i = blockIdx.x; i < p.n_items && ok; i += gridDim.x, ++n) {
         const uint32_t buf = n & 1u, aph = (n >> 1) & 1u;
-        ok = mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.acc_empty[buf]), aph ^ 1u, abort_flag));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d = tmem_base + buf * 32u;
@@ -147,21 +150,23 @@ __global__ void __launch_bounds__(kThreads, 2) tile_grad_kernel(const __grid_con
         for (int s = 0; s < p.n_slices; ++s, ++g) {
           const int stage = (int)(g % kStages);
           const uint32_t phase = (g / kStages) & 1u;
-          ok = mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag));
           if (!ok) break;
           tc_fence_after();
           const uint32_t base = ring + (uint32_t)stage * kStageBytes;
           const uint64_t ad = smem_desc(hi, base), bd = smem_desc(hi, base + 4u * kBlockBytes);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {  // 32 bytes of n per MMA: the start address moves inside the swizzle atom
-            issue<KIND>(d, ad + 2u * kk, bd + 2u * kk, idesc, acc);
+            if (leader) issue<KIND>(d, ad + 2u * kk, bd + 2u * kk, idesc, acc);
             acc = 1u;
           }
-          tc_commit(smem_u32(&bars.empty[stage]));
+          if (leader) tc_commit(smem_u32(&bars.empty[stage]));
         }
         if (!ok) break;
-        if (p.n_slices > 0) tc_commit(smem_u32(&bars.acc_full[buf]));
-        else mbar_arrive(smem_u32(&bars.acc_full[buf]));
+        if (leader) {
+          if (p.n_slices > 0) tc_commit(smem_u32(&bars.acc_full[buf]));
+          else mbar_arrive(smem_u32(&bars.acc_full[buf]));
+        }
       }
     }
     __syncwarp();
