@@ -1230,7 +1230,7 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
 }
 
 struct DeviceInfo {
-  int sms = 0, cc_major = 0, cc_minor = 0, max_smem = 0;
+  int sms = 0, cc_major = 0, cc_minor = 0, max_smem = 0, smem_per_sm = 0;
   bool ok = false;
 };
 static DeviceInfo device_info() {
@@ -1246,6 +1246,7 @@ static DeviceInfo device_info() {
     cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
     cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
     cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaDeviceGetAttribute(&d.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
     d.ok = true;
     cache[dev] = d;
   }
@@ -1351,9 +1352,14 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   const int producer_warps = (shape == 1) ? Wide::PW : ((shape >= 4) ? 1 : Slim::PW);
   const int ctas_per_sm = (slim || shape == 5) ? 4 : (shape >= 3 ? 3 : ((np == 4) ? 1 : Wide::CTAS_PER_SM));
   int group = a->tiles_per_stage;  // 0 = default
-  if (group == 0) group = (np == 1) ? 4 : 2;  // few, large ring stages beat a deep ring of small ones
+  // What a CTA streams is bounded by the bytes its ring keeps in flight over a stage's round trip, so the defaults fill
+  // the shared memory four CTAs per SM leave each other: nine (tile + panel) units as 3 stages x 3 for one 8-bit panel per
+  // item (swept on B200, headline / 70 % / 16384^2: 2 x 4 units 7.02 / 11.06 / 69.9 us, 3 x 3: 6.76 / 10.21 / 65.1,
+  // 4 x 2: 6.96 / 10.87 / 69.4, 9 x 1: 8.64 / 16.2 / 111); stages of one or two tiles pay the fixed cost of a stage too often
+  if (group == 0) group = (np == 1) ? 3 : 2;
   if (a->tiles_per_stage == 0 && floating) group = (es == 2 && np == 1) ? 2 : 1;
-  if (a->tiles_per_stage == 0 && a->tile_terms > 1) group = (np == 1) ? 3 : 1;   // wider tiles: keep four CTAs per SM
+  // wider tiles (an FP8 tile stored as two or three terms): 3 stages x 2 (headline 7.66 us, 2 x 3: 7.93)
+  if (a->tiles_per_stage == 0 && a->tile_terms > 1) group = (np == 1) ? 2 : 1;
   if (group < 1 || group > 8) return VOID_ERR_BAD_ARG;
   if (drain && np == 1 && shape != 1 && a->tiles_per_stage == 0) group = 2;
   int drain_tmem = 32;   // the largest power of two that lets ctas_per_sm CTAs share the SM's 512 columns
@@ -1362,17 +1368,6 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   int terms = a->tile_terms == 0 ? 1 : a->tile_terms;
   if (terms < 1 || terms > 3) return VOID_ERR_BAD_ARG;
   if (terms > 1 && (kind != VOID_KIND_F8E4M3 || drain || tr)) return VOID_ERR_BAD_ARG;  // FP8 row-accumulate only
-  const int stage_bytes = group * (np * kPanelBytes + kTileBytes * terms) * es;
-  int stages = a->stages;
-  if (stages == 0) {
-    const int budget = (216 * 1024) / ctas_per_sm - 2048;
-    stages = budget / stage_bytes;
-    if (stages > 8) stages = 8;
-  }
-  // A producer warp may run up to (producer warps - 1) groups ahead of the consumer's order; the
-  // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
-  // hold at least one stage per producer warp.
-  if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
   // 16-bit outputs of the slim row-accumulate kernel leave through a staging tile (32 x 128 x 2 bytes behind the
   // ring) and a tiled TMA store, when C qualifies as a tensor for the copy engine (16-byte aligned base and pitch)
   // (with a plan, whole-row segments take this route and the pieces of split rows the ordinary one)
@@ -1380,7 +1375,22 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
                          a->worker_partials == nullptr && (a->flags & 2) == 0 &&
                          (a->out_dtype == VOID_OUT_F16 || a->out_dtype == VOID_OUT_BF16) &&
                          (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0 && ((a->ldc * 2) & 15) == 0;
-  const int smem_bytes = stages * stage_bytes + 1024 + (tma_store ? kTile * kPanelN * 2 : 0);
+  const int stage_bytes = group * (np * kPanelBytes + kTileBytes * terms) * es;
+  const int staging_bytes = tma_store ? kTile * kPanelN * 2 : 0;
+  int stages = a->stages;
+  if (stages == 0) {
+    // dynamic shared memory a CTA may use so that ctas_per_sm of them fit an SM: the SM's bytes less the kilobyte
+    // the system keeps per CTA and the kernel's static variables, less this kernel's 1 KB of slack for alignment
+    // and the staging tile
+    const int budget = dev.smem_per_sm / ctas_per_sm - 1024 - 640 - 1024 - staging_bytes;
+    stages = budget / stage_bytes;
+    if (stages > 8) stages = 8;
+  }
+  // A producer warp may run up to (producer warps - 1) groups ahead of the consumer's order; the
+  // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
+  // hold at least one stage per producer warp.
+  if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
+  const int smem_bytes = stages * stage_bytes + 1024 + staging_bytes;
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
   SpmmParams p;
