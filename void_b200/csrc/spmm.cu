@@ -687,7 +687,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
           if (TRACE && leader && i == begin && gidx < 8) stamp<TRACE>(p, 48 + gidx);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[stage]), phase, ctl));
           if (!ok) break;
-          if (TRACE && leader && i == begin && gidx < 16) stamp<TRACE>(p, 16 + gidx);
+          if (TRACE && leader && i == begin && gidx < 12) stamp<TRACE>(p, 16 + gidx);   // slots 28 .. 31: last arriver of a split row
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
           uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
