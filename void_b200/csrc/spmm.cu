@@ -17,14 +17,15 @@
 // warp issues the MMAs and owns the tensor-memory allocation, epilogue warps read accumulators back
 // (one or two warps per 32-lane TMEM quadrant), apply scales / bias / activation and store C.
 //
-// The ring moves GROUPS of up to `group` consecutive tiles of a tile row per stage.  Measured on
-// B200, one turn of a stage by one thread (wait for the slot, expect_tx, issue the copies) costs
-// about 300 ns whatever the bytes, so the stream is latency-bound on the issuing thread, not on
-// the copy engine: a group needs one wait + one expect_tx + one bulk copy (its tiles are
-// contiguous in the packed store) and one tiled TMA per tile, the TMAs issued by different lanes
-// in the same instruction, and the producer warps take the groups round-robin so that several
-// stage turns are in flight at once.  When N is a whole number of 128-byte column blocks the TMA
-// is 3-D (B viewed as [column block][k][128 bytes]) and fetches all panels of the work item at once.
+// The ring moves GROUPS of up to `group` consecutive tiles of a tile row per stage: a group needs one
+// wait + one expect_tx + one bulk copy (its tiles are contiguous in the packed store) and one tiled TMA
+// per tile, the TMAs issued by different lanes in the same instruction, and the producer warps take the
+// groups round-robin so that several stage turns are in flight at once.  Measured on B200, a stage's
+// round trip (copies requested, landed, MMAs issued and retired, stage handed back) takes 1.2 - 1.3 us
+// whatever its size, so a CTA streams what its ring holds per round trip and the launcher gives the
+// ring all the shared memory that four CTAs per SM leave each other.  When N is a whole number of
+// 128-byte column blocks the TMA is 3-D (B viewed as [column block][k][128 bytes]) and fetches all panels
+// of the work item at once.
 //
 // Two kernels share this pipeline:
 //   spmm_rowacc_kernel  one accumulator per (tile row, column chunk), scaled once by the
@@ -70,8 +71,8 @@ constexpr int kMaxSlots = 16;
 // Warp roles of a CTA: PW producer warps (0..PW-1) stream tiles and panels, warp PW issues the MMAs
 // and owns the TMEM allocation, EW epilogue warps follow (EW/4 per TMEM lane quadrant, each taking
 // 32/(EW/4) accumulator columns).  Two shapes are built: a wide one (4 + 1 + 8 warps, two CTAs per
-// SM) and a slim one (2 + 1 + 4 warps, four CTAs per SM).  The pipeline is latency-bound on the
-// single MMA-issuing thread of a CTA, so four slim CTAs per SM move more tiles than two wide ones.
+// SM) and a slim one (2 + 1 + 4 warps, four CTAs per SM).  A CTA's stream is bound by the round trip of
+// its ring, so four slim CTAs per SM move more tiles than two wide ones.
 template <int PW_, int EW_, int CTAS_>
 struct Shape {
   static constexpr int PW = PW_;
