@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define VOID_B200_ABI_VERSION 4
+#define VOID_B200_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define VOID_API __attribute__((visibility("default")))
@@ -347,6 +347,13 @@ typedef struct void_spmm_args {
   void* peer_partials[8];
   int32_t* peer_counters[8];
   void* peer_out[8];
+  /* Launches without a plan: the order in which the persistent CTAs take the tile rows, int32 [nbr], a permutation of
+   * 0 .. nbr - 1 (work item i is tile row row_order[i / chunks], column chunk i % chunks), or NULL for 0, 1, 2, ...
+   * The CTAs that start first take the first items, so tile rows sorted by falling tile count give the longest rows
+   * the earliest start and leave the shortest for the CTAs that share an SM with the most others.  The result does not
+   * depend on the order.  Entries are clamped to 0 .. nbr - 1; a list that is not a permutation leaves tile rows of C
+   * unwritten (and writes others twice) but reads and writes nothing outside the tensors. */
+  const int32_t* row_order;
 } void_spmm_args;
 
 VOID_API int void_spmm_i8(const void_spmm_args* args, void_stream_t stream);

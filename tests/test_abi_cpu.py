@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_library_loads_and_reports_errors():
     lib = _lib.load()
-    assert lib.void_b200_abi_version() == _lib.ABI_VERSION == 4
+    assert lib.void_b200_abi_version() == _lib.ABI_VERSION == 5
     assert lib.void_strerror(0) == b"ok"
     assert b"alignment" in lib.void_strerror(-2)
     with pytest.raises(_lib.VoidB200Error):

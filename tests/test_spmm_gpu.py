@@ -116,6 +116,41 @@ def test_int8_spmm_launch_shapes_agree():
     void.check_device_status()
 
 
+def test_row_order_changes_the_schedule_only():
+    """Launches without a plan take the tile rows by falling tile count (PackedTiles.row_order); the result has the
+    bits of the launch that takes them in their own order, with one and several work items per CTA, and a list
+    with entries outside the tensor is clamped instead of followed."""
+    from void_b200 import _lib, _spmm
+    for nbr, nbc, n, grid in ((37, 29, 384, 0), (37, 29, 384, 5), (128, 128, 512, 0), (3, 40, 100, 0)):
+        mask = workloads.uniform_mask(nbr, nbc, 0.8, seed=nbr)
+        mask[nbr // 2] = False
+        w = workloads.block_sparse(mask, n, seed=nbr)
+        q = void.quantize_void_tensor(w.a)
+        bq, bs = void.quantize_cols_int8(w.b)
+        p = q.packed()
+        counts = (p.row_ptr[1:] - p.row_ptr[:-1]).cpu().numpy()
+        order = p.row_order.cpu().numpy()
+        assert sorted(order.tolist()) == list(range(nbr)) and np.all(np.diff(counts[order]) <= 0)
+        outs = []
+        for srt in (False, True):
+            out = torch.full((nbr * 32, n), 7.0, dtype=torch.float16, device="cuda")
+            _spmm.spmm(p, bq, out, scale_mode=_lib.SCALE_ROW_MEAN, col_scale=bs, grid=grid, sorted_rows=srt)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), (nbr, nbc, n, grid)
+    # a list that is not a permutation: nothing outside C is touched, the launch ends normally
+    bad = p.row_order.clone()
+    bad[0], bad[1] = -5, 10 ** 6
+    keep, p.row_order = p.row_order, bad
+    try:
+        guard = torch.full((nbr * 32 + 64, n), 7.0, dtype=torch.float16, device="cuda")
+        _spmm.spmm(p, bq, guard[32:32 + nbr * 32], scale_mode=_lib.SCALE_ROW_MEAN, col_scale=bs)
+        torch.cuda.synchronize()
+        assert bool((guard[:32] == 7.0).all()) and bool((guard[32 + nbr * 32:] == 7.0).all())
+    finally:
+        p.row_order = keep
+    void.check_device_status()
+
+
 @pytest.mark.parametrize("case", [(16, 16, 256, 0, torch.float16, 0), (9, 7, 200, 5, torch.bfloat16, 2),
                                   (5, 5, 128, 31, torch.float16, 1), (4, 4, 8, 0, torch.bfloat16, 3)])
 def test_staged_tma_store_equals_direct_stores(case):

@@ -14,7 +14,7 @@ from . import build as _build
 _LOCK = threading.Lock()
 _LIB = None
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 c_i32, c_i64, c_f32, c_vp, c_sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
 
 # enums of include/void_b200.h
@@ -44,6 +44,7 @@ class SpmmArgs(ctypes.Structure):
         ("panels_per_item", c_i32), ("stages", c_i32), ("grid", c_i32), ("tiles_per_stage", c_i32),
         ("trace", c_vp), ("cta_shape", c_i32), ("flags", c_i32), ("row_bias", c_vp), ("transposed", c_i32), ("test_hooks", c_i32), ("tile_terms", c_i32), ("reserved", c_i32), ("n_peers", c_i32), ("peer_slots", c_i32),
         ("peer_partials", c_vp * 8), ("peer_counters", c_vp * 8), ("peer_out", c_vp * 8),
+        ("row_order", c_vp),
     ]
 
 

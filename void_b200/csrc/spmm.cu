@@ -105,6 +105,7 @@ struct SpmmParams {
   const int32_t* tile_cols;
   const float* tile_scales;
   const int32_t* row_ptr;
+  const int32_t* row_order;  // launches without a plan: tile row of the k-th row taken, or null for k
   const float* row_scale;
   int nbr, nbc, n_chunks, N, M;
   long long nnz;
@@ -171,8 +172,13 @@ __device__ __forceinline__ Seg load_seg(const SpmmParams& p, int i) {
     s.row = a.x; s.chunk = a.y; s.t0 = a.z; s.t1 = a.w;
     s.nseg = b.x; s.slot0 = b.y; s.my_idx = b.z; s.ctr = b.w;
   } else {
-    s.row = i / p.n_chunks;
-    s.chunk = i - s.row * p.n_chunks;
+    const int k = i / p.n_chunks;   // k-th tile row taken
+    s.chunk = i - k * p.n_chunks;
+    s.row = k;
+    if (p.row_order != nullptr) {
+      const int r = __ldg(p.row_order + k);
+      s.row = r < 0 ? 0 : (r >= p.nbr ? p.nbr - 1 : r);
+    }
     s.t0 = __ldg(p.row_ptr + s.row);
     s.t1 = __ldg(p.row_ptr + s.row + 1);
     s.nseg = 1; s.slot0 = 0; s.my_idx = 0; s.ctr = 0;
@@ -1399,6 +1405,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.tile_cols = a->tile_cols;
   p.tile_scales = a->tile_scales;
   p.row_ptr = a->row_ptr;
+  p.row_order = a->segs == nullptr ? a->row_order : nullptr;
   p.row_scale = a->row_scale;
   p.nbr = a->nbr;
   p.nbc = a->nbc;
