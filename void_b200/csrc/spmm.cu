@@ -137,6 +137,7 @@ struct SpmmParams {
   int terms;    // packed tiles per stored tile: 1, or 2 / 3 when an FP8 tile is stored as a sum of E4M3 terms
   int group;    // tiles per ring stage
   int stages;   // ring depth
+  int last_group;   // tiles of the ring's last stage (1 .. group): the shared memory left over by the full stages
   int use3d;    // B panels of a tile fetched by one 3-D TMA
   int tma_store;  // 16-bit outputs leave through a staging tile in shared memory and a tiled TMA store
   int tmem_cols;  // tensor-memory columns of the drain kernel (256: two CTAs per SM, 512: one)
@@ -447,9 +448,16 @@ template <int ES>
 __device__ __forceinline__ uint32_t panel_off(const SpmmParams& p, int j, int q) {
   return (uint32_t)(j * p.np + q) * (kPanelBytes * ES);
 }
+// A stage holds the panels of its tiles first, then the tiles; `cap` is the stage's capacity in tiles
 template <int ES>
-__device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int j) {
-  return (uint32_t)(p.group * p.np) * (kPanelBytes * ES) + (uint32_t)(j * p.terms) * (kTileBytes * ES);
+__device__ __forceinline__ uint32_t tile_off(const SpmmParams& p, int cap, int j) {
+  return (uint32_t)(cap * p.np) * (kPanelBytes * ES) + (uint32_t)(j * p.terms) * (kTileBytes * ES);
+}
+// Capacity of a ring stage: every stage takes p.group tiles except the last, which takes what is left of the
+// shared memory (p.last_group).  The groups of a tile row follow the stages they fall on: a group is
+// min(capacity of its stage, tiles left in the row) consecutive tiles.
+__device__ __forceinline__ int stage_cap(const SpmmParams& p, int stage) {
+  return stage == p.stages - 1 ? p.last_group : p.group;
 }
 
 // Producer warp `pw` of C::PW: the CTA's groups of tiles are numbered in the order the MMA warp
@@ -470,8 +478,10 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
   if (TRACE && pw == 0 && lane == 0) stamp<TRACE>(p, 56);   // producer starts
   int begin, end, step;
   seg_range(p, begin, end, step);
-  const int G = p.group;
-  int g = 0;  // groups of all earlier segments
+  const int S = p.stages;
+  // position of the next group in the ring: its stage, the parity of the stage's use, the warp it belongs to
+  int stage = 0, owner = 0, gcount = 0;
+  uint32_t phase = 0;
   Seg seg_next = {};  // the next segment's descriptor is fetched one item ahead
   if (begin < end) seg_next = load_seg(p, begin);
   for (int i = begin; i < end; i += step) {
@@ -480,68 +490,78 @@ __device__ __forceinline__ void producer_loop(const SpmmParams& p, const CUtenso
     const int npan = panels_in_chunk(p, s.chunk);
     const int n0 = s.chunk * p.np * kPanelN;
     const uint32_t unit_bytes = (uint32_t)((kTileBytes * p.terms + ((p.use3d && !TR) ? p.np : npan) * kPanelBytes) * ES);
-    const int ngroups = (s.t1 - s.t0 + G - 1) / G;
     if (TRACE && i == begin && pw == 0 && lane == 0) {
       asm volatile("" ::"r"(s.t1) : "memory");
       stamp<TRACE>(p, 57);   // the row's tile range has arrived
     }
-    int k = pw - g % C::PW;
-    if (k < 0) k += C::PW;
-    // block column of this lane's tile in the warp's next group, fetched one group ahead
+    // block column of this lane's tile in the warp's next group, fetched one group of its own ahead; (ct, cs):
+    // first tile and stage of that group
+    int ct = s.t0, cs = stage;
+    for (int o = owner; o != pw && ct < s.t1; o = (o + 1 == C::PW) ? 0 : o + 1) {
+      ct += stage_cap(p, cs);
+      cs = (cs + 1 == S) ? 0 : cs + 1;
+    }
     int col = 0;
-    if (k < ngroups && lane < G && s.t0 + k * G + lane < s.t1) col = __ldg(p.tile_cols + s.t0 + k * G + lane);
+    if (ct + lane < s.t1 && lane < stage_cap(p, cs)) col = __ldg(p.tile_cols + ct + lane);
     if (TRACE && i == begin && pw == 0 && lane == 0) {
       asm volatile("" ::"r"(col) : "memory");
       stamp<TRACE>(p, 58);   // the first block columns have arrived
     }
-    for (; k < ngroups; k += C::PW) {
-      const int gi = g + k;
-      const int stage = gi % p.stages;
-      const uint32_t phase = (uint32_t)(gi / p.stages) & 1u;
-      const int t = s.t0 + k * G;
-      const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
-      const int kn = k + C::PW;
-      int col_next = 0;
-      if (kn < ngroups && lane < G && s.t0 + kn * G + lane < s.t1) col_next = __ldg(p.tile_cols + s.t0 + kn * G + lane);
-      const uint32_t full = smem_u32(&bars->full[stage]);
-      const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
-      // test hook: the first group of the CTA is never delivered, so the consumer's bounded wait runs out
-      const bool drop = p.drop_group != 0 && gi == 0;
-      int ok = 1;
-      if (lane == 0) {
-        ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, ctl) ? 1 : 0;
-        if (ok && !drop) {
-          mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
-          bulk_load(sbase + tile_off<ES>(p, 0), p.tiles + (size_t)t * (size_t)(kTileBytes * ES * p.terms),
-                    (uint32_t)(gcnt * p.terms) * (kTileBytes * ES), full);
+    int k = 0;   // group of the segment
+    for (int t = s.t0; t < s.t1; ++k, ++gcount) {
+      const int cap = stage_cap(p, stage);
+      const int gcnt = (s.t1 - t) < cap ? (s.t1 - t) : cap;
+      if (owner == pw) {
+        // this warp's group after this one
+        int nt = t, ns = stage;
+        for (int o = 0; o < C::PW && nt < s.t1; ++o) {
+          nt += stage_cap(p, ns);
+          ns = (ns + 1 == S) ? 0 : ns + 1;
         }
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) return;
-      if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 59);   // tiles of the first group requested
-      if (!waited) {  // B may be the output of the previous kernel
-        grid_dependency_wait();
-        waited = true;
-      }
-      if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 60);   // past the wait on the previous kernel
-      if (lane < gcnt && !drop) {
-        if (TR) {
-          // B stored transposed ([N, K], k contiguous): one box of 128 rows of n x 32 k per panel
-          for (int q = 0; q < npan; ++q)
-            tma_load_2d(sbase + panel_off<ES>(p, lane, q), tmap, col * kTile, n0 + q * kPanelN, full);
-        } else if (p.use3d) {
-          tma_load_3d(sbase + panel_off<ES>(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np * ES, full);
-        } else {
-          // one copy per 128-byte-wide block of columns: ES blocks of 128 / ES columns per panel
-          for (int q = 0; q < npan * ES; ++q)
-            tma_load_2d(sbase + panel_off<ES>(p, lane, 0) + (uint32_t)q * kPanelBytes, tmap,
-                        n0 + q * (kPanelN / ES), col * kTile, full);
+        int col_next = 0;
+        if (nt + lane < s.t1 && lane < stage_cap(p, ns)) col_next = __ldg(p.tile_cols + nt + lane);
+        const uint32_t full = smem_u32(&bars->full[stage]);
+        const uint32_t sbase = ring_base + (uint32_t)stage * stage_bytes;
+        // test hook: the first group of the CTA is never delivered, so the consumer's bounded wait runs out
+        const bool drop = p.drop_group != 0 && gcount == 0;
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, ctl) ? 1 : 0;
+          if (ok && !drop) {
+            mbar_expect_tx(full, unit_bytes * (uint32_t)gcnt);
+            bulk_load(sbase + tile_off<ES>(p, cap, 0), p.tiles + (size_t)t * (size_t)(kTileBytes * ES * p.terms),
+                      (uint32_t)(gcnt * p.terms) * (kTileBytes * ES), full);
+          }
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;
+        if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 59);   // tiles of the first group requested
+        if (!waited) {  // B may be the output of the previous kernel
+          grid_dependency_wait();
+          waited = true;
+        }
+        if (TRACE && i == begin && pw == 0 && lane == 0 && k == 0) stamp<TRACE>(p, 60);   // past the wait on the previous kernel
+        if (lane < gcnt && !drop) {
+          if (TR) {
+            // B stored transposed ([N, K], k contiguous): one box of 128 rows of n x 32 k per panel
+            for (int q = 0; q < npan; ++q)
+              tma_load_2d(sbase + panel_off<ES>(p, lane, q), tmap, col * kTile, n0 + q * kPanelN, full);
+          } else if (p.use3d) {
+            tma_load_3d(sbase + panel_off<ES>(p, lane, 0), tmap, 0, col * kTile, s.chunk * p.np * ES, full);
+          } else {
+            // one copy per 128-byte-wide block of columns: ES blocks of 128 / ES columns per panel
+            for (int q = 0; q < npan * ES; ++q)
+              tma_load_2d(sbase + panel_off<ES>(p, lane, 0) + (uint32_t)q * kPanelBytes, tmap,
+                          n0 + q * (kPanelN / ES), col * kTile, full);
+          }
+        }
+        if (TRACE && lane == 0 && i == begin && k < 16) stamp<TRACE>(p, 32 + k);
+        col = col_next;
       }
-      if (TRACE && lane == 0 && i == begin && k < 16) stamp<TRACE>(p, 32 + k);
-      col = col_next;
+      t += gcnt;
+      owner = (owner + 1 == C::PW) ? 0 : owner + 1;
+      if (++stage == S) { stage = 0; phase ^= 1u; }
     }
-    g += ngroups;
   }
   if (!waited) grid_dependency_wait();
 }
@@ -637,7 +657,9 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
   const int lane = threadIdx.x & 31;
   const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr int ES = Elem<KIND>::ES;
-  const uint32_t stage_bytes = (uint32_t)(p.group * (p.np * kPanelBytes + kTileBytes * p.terms) * ES);
+  const uint32_t unit_smem = (uint32_t)((p.np * kPanelBytes + kTileBytes * p.terms) * ES);
+  const uint32_t stage_bytes = (uint32_t)p.group * unit_smem;   // the last stage may be shorter (p.last_group tiles)
+  const uint32_t ring_bytes = (uint32_t)((p.stages - 1) * p.group + p.last_group) * unit_smem;
   const uint32_t acc_cols = (uint32_t)p.np * 32u;  // TMEM columns of one accumulator buffer
   uint32_t tmem_cols = 32;
   while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
@@ -662,8 +684,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
       if (!p.a_stable) grid_dependency_wait();
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
-      const int G = p.group, S = p.stages, np = p.np, terms = p.terms;
-      const uint32_t tiles_at = (uint32_t)(G * np) * (kPanelBytes * ES);
+      const int S = p.stages, np = p.np, terms = p.terms;
       constexpr uint64_t kPanelStep = (kPanelBytes * ES) >> 4, kTileStep = (kTileBytes * ES) >> 4;
       // one MMA covers 32 bytes of k: 32 / ES k-rows of the panel (8-row groups 1024 bytes apart) and two
       // 16-byte k-chunks of the packed tile (128 bytes apart)
@@ -689,15 +710,17 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
         const uint32_t d0 = tmem_base + buf * acc_cols;
         uint32_t acc = 0u;
         int gidx = 0;
-        for (int t = s.t0; t < s.t1; t += G, ++gidx) {
-          const int gcnt = (s.t1 - t) < G ? (s.t1 - t) : G;
+        for (int t = s.t0; t < s.t1; ++gidx) {
+          const int cap = stage_cap(p, stage);
+          const int gcnt = (s.t1 - t) < cap ? (s.t1 - t) : cap;
+          t += gcnt;
           if (TRACE && leader && i == begin && gidx < 8) stamp<TRACE>(p, 48 + gidx);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.full[stage]), phase, ctl));
           if (!ok) break;
           if (TRACE && leader && i == begin && gidx < 12) stamp<TRACE>(p, 16 + gidx);   // slots 28 .. 31: last arriver of a split row
           tc_fence_after();
           uint64_t ad = smem_desc(hi_a, sbase);
-          uint64_t bd = smem_desc(hi_b, sbase + tiles_at);
+          uint64_t bd = smem_desc(hi_b, sbase + tile_off<ES>(p, cap, 0));
           for (int j = 0; j < gcnt; ++j) {
             uint64_t adq = ad;
             uint32_t d = d0;
@@ -741,7 +764,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) spmm_rowacc_kernel
     const int m_first = half * C::COLS;
     const OutDesc od = out_desc(p);
     // staging tile of the TMA-store epilogue: behind the ring
-    const uint32_t stage_u32 = ring_base + (uint32_t)p.stages * stage_bytes;
+    const uint32_t stage_u32 = ring_base + ring_bytes;
     uint16_t* stage_tile = reinterpret_cast<uint16_t*>(smem_raw + (stage_u32 - smem_u32(smem_raw)));
     bool store_pending = false;
     // the column scales and biases this role reads and the C it writes may be the previous kernel's; the index
@@ -1071,7 +1094,7 @@ __global__ void __launch_bounds__(C::THREADS, (NP == 4) ? 1 : C::CTAS_PER_SM) sp
       if (!p.a_stable) grid_dependency_wait();
       const uint32_t idesc = p.idesc;
       const uint64_t hi_a = p.desc_hi_a, hi_b = p.desc_hi_b;
-      const int G = p.group, S = p.stages;
+      const int G = p.group, S = p.stages;   // (the per-tile kernel runs with stages of equal size)
       const uint32_t tiles_at = (uint32_t)(G * NP) * kPanelBytes;
       constexpr uint64_t kPanelStep = kPanelBytes >> 4, kTileStep = kTileBytes >> 4;
       int begin, end, step;
@@ -1393,11 +1416,24 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
     stages = budget / stage_bytes;
     if (stages > 8) stages = 8;
   }
+  // The shared memory the full stages leave over becomes a shorter last stage (row-accumulate kernel, ring sized
+  // here) when it adds at least a fifth to the tiles in flight: 2 + 2 + 1 tiles of two 8-bit panels each take 63.8 us
+  // at 16384^2 and 64.0 on an eight-rank shard of 65536^2 against 68.9 and 70.8 with 2 + 2; a seventh tile behind
+  // 3 x 2 FP8 tiles of two terms costs more in stage turns than it brings (7.49 against 7.44 us, 13.54 against 13.25)
+  int last_group = group;
+  if (a->stages == 0 && !drain) {
+    const int budget = dev.smem_per_sm / ctas_per_sm - 1024 - 640 - 1024 - staging_bytes;
+    const int left = (budget - stages * stage_bytes) / (stage_bytes / group);
+    if (left >= 1 && 5 * left >= stages * group && stages < kMaxStages) {
+      last_group = left < group ? left : group;
+      stages += 1;
+    }
+  }
   // A producer warp may run up to (producer warps - 1) groups ahead of the consumer's order; the
   // parity of a ring barrier only tells two consecutive uses of a stage apart, so the ring must
   // hold at least one stage per producer warp.
   if (stages < producer_warps || stages > kMaxStages) return VOID_ERR_BAD_ARG;
-  const int smem_bytes = stages * stage_bytes + 1024 + staging_bytes;
+  const int smem_bytes = ((stages - 1) * group + last_group) * (stage_bytes / group) + 1024 + staging_bytes;
   if (smem_bytes > dev.max_smem) return VOID_ERR_SHAPE;
 
   SpmmParams p;
@@ -1448,6 +1484,7 @@ static int spmm_launch(const void_spmm_args* a, int kind, cudaStream_t stream) {
   p.terms = terms;
   p.group = group;
   p.stages = stages;
+  p.last_group = last_group;
   p.use3d = (!tr && a->N % (kPanelN / es) == 0) ? 1 : 0;
   p.tmem_cols = drain_tmem;
   p.tma_store = tma_store ? ((a->flags & 16) ? 1 : 2) : 0;   // 2: one store per epilogue warp; 1: one per tile
