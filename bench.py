@@ -840,13 +840,16 @@ def main():
             sl["ev_out"].record(st_k)
 
     e2e_steps = max(3, min(K_steps, 200))
+    # the pipelined legs run long enough for the filling of the pipeline (DEPTH steps, a few hundred microseconds) to
+    # be a small share of the timed region whatever K is: at least 400 steps
+    e2e_pipe_steps = max(2 * e2e_steps, 400)
     e2e_serial_ms = time_e2e(lambda i: e2e_step_serial(), e2e_steps)
-    e2e_streams_ms = time_e2e(e2e_step_pipelined, 2 * e2e_steps)
+    e2e_streams_ms = time_e2e(e2e_step_pipelined, e2e_pipe_steps)
     e2e_ms = e2e_streams_ms
     if slot_graphs is not None:
         for sl in slots:
             sl["h_c"].zero_()                              # the check below must see what the graphs wrote
-        e2e_ms = time_e2e(e2e_step_graph, 2 * e2e_steps)
+        e2e_ms = time_e2e(e2e_step_graph, e2e_pipe_steps)
         if e2e_ms > e2e_streams_ms:
             e2e_ms, e2e_mode = e2e_streams_ms, "host wall clock, %d steps in flight (copy-in / operator / copy-out streams)" % DEPTH
     e2e_check = bool(torch.equal(slots[1]["h_c"], slots[0]["h_c"]) and
@@ -939,6 +942,7 @@ def main():
                     "h2d_bytes_per_step": int(h_b.numel() + h_s.numel() * 4),
                     "d2h_bytes_per_step": int(h_c.numel() * h_c.element_size()),
                     "mode": e2e_mode + E2E_WHAT,
+                    "timed_steps": e2e_pipe_steps,
                     "one_step_at_a_time_ms": e2e_serial_ms,
                     "one_step_at_a_time_value": ops_per_step / (e2e_serial_ms * 1e-3) / 1e12,
                     "results_identical_across_slots": e2e_check},
