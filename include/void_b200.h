@@ -285,7 +285,8 @@ typedef struct void_spmm_args {
   int32_t* status;
   /* launch shape; 0 = library default                                                   */
   int32_t panels_per_item; /* 128-column panels of B per work item: 1, 2 or 4            */
-  int32_t stages;          /* shared-memory ring depth                                   */
+  int32_t stages;          /* shared-memory ring depth; 0: what fits beside the other CTAs of the SM, plus a
+                            * shorter last stage from the bytes left over where that adds a fifth to the ring */
   int32_t grid;            /* CTAs to launch without a plan                              */
   int32_t tiles_per_stage; /* consecutive tiles of a row moved per ring stage: 1 ... 8         */
   /* diagnostics: NULL for every ordinary launch.  Not NULL selects a separately compiled diagnostic kernel
